@@ -1,4 +1,4 @@
-"""A small generation library for one NVIDIA B200: the Llama 3 dense decoder, the Pogezen decoder and the Vuladra decoder.
+"""A small generation library for one NVIDIA B200: the Llama 3 dense decoder, the Pogezen, Vuladra and Tonovik decoders.
 
 Everything between a request's token ids and its next token: typed configuration and
 architecture registry, weights by tensor name, layers put together from parts, a paged
@@ -7,10 +7,10 @@ and hand-written sm_100a CUDA kernels underneath.  The GPU is required to run a 
 describing one (configuration, weight table, cache bookkeeping) needs none.
 """
 from . import cache, config, engine, parts, weights  # noqa: F401
-from .config import LlamaConfig, PogezenConfig, VuladraConfig, load_config, register_architecture
+from .config import LlamaConfig, PogezenConfig, TonovikConfig, VuladraConfig, load_config, register_architecture
 
 __version__ = "0.1.0"
-__all__ = ["cache", "config", "engine", "parts", "weights", "LlamaConfig", "PogezenConfig", "VuladraConfig", "load_config", "register_architecture"]
+__all__ = ["cache", "config", "engine", "parts", "weights", "LlamaConfig", "PogezenConfig", "VuladraConfig", "TonovikConfig", "load_config", "register_architecture"]
 
 
 def load(model: str, dtype: str = "bfloat16", max_tokens: int = 4096, device: int = 0, **kw):

@@ -107,8 +107,8 @@ int hb_relu2(const void* in, int in_dtype, long long ldi, void* out, int out_dty
 // Biases, rotation, unit norm, cache append (keys [pages][kv][64][head_dim], values [pages][kv][64][v_dim]);
 // v_mode 0: values as they are; 1: also kept in v_first [tokens][kv * v_dim]; 2: mixed with v_first by v_lambda[0]
 int hb_qkv_prepare(const void* proj, int proj_dtype, long long ldp, const float* bias, const float* table, int rot,
-                   int n_heads, int n_kv_heads, int head_dim, int v_dim, int unit_norm, float eps, void* q_out, int q_dtype,
-                   long long ldq, void* k_cache, void* v_cache, int cache_dtype, const int* page_table, int pt_width,
+                   int n_heads, int n_kv_heads, int head_dim, int v_dim, int unit_norm, const float* q_norm_w, const float* k_norm_w,
+                   float eps, void* q_out, int q_dtype, long long ldq, void* k_cache, void* v_cache, int cache_dtype, const int* page_table, int pt_width,
                    const int* tok_seq, const int* positions, int n_tokens, int n_pages, int append, const float* v_lambda,
                    float* v_first, int v_mode, int* status, void* stream);
 // out [tokens][heads][all_values ? kv heads : 1][v_dim] float32
@@ -117,7 +117,7 @@ int hb_attention_sink(const void* q, int q_dtype, long long ldq, const void* k_c
                       int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first,
                       int all_values, int n_pages, int* status, void* stream);
 int hb_head_mix(const float* partial, const float* mix, void* out, int out_dtype, long long ldo, int n_tokens, int n_heads,
-                int n_kv_heads, int v_dim, int n_val, int ones, void* stream);
+                int n_kv_heads, int v_dim, int n_val, int ones, const float* gate, long long ldg, void* stream);
 // One block per (token, key split) for all heads; see attention_sink.cu.  hb_attention_heads_variant: 0 when the sizes are not built.
 int hb_attention_heads_variant(int n_heads, int n_kv_heads, int head_dim, int v_dim, int cache_dtype, int allow_mma);
 int hb_attention_heads_writes_output(int n_heads, int n_kv_heads, int head_dim, int v_dim, int cache_dtype, int allow_mma);
@@ -127,7 +127,7 @@ int hb_attention_heads(const void* q, int q_dtype, long long ldq, const void* k_
                        int v_dim, float scale, int window, int keep_first, int splits, int n_pages, int allow_mma, int* status,
                        void* stream);
 int hb_head_mix_splits(const float* partial, const float* ml, const float* mix, void* out, int out_dtype, long long ldo, int n_tokens,
-                       int n_heads, int n_kv_heads, int v_dim, int splits, int ones, void* stream);
+                       int n_heads, int n_kv_heads, int v_dim, int splits, int ones, const float* gate, long long ldg, void* stream);
 // Flash-style on the tensor cores for steps of many tokens (bfloat16, head sizes 64 or 128); out float32
 // [tokens][heads][n_val][v_dim], n_val = kv heads (every value head) or 1 (the head's own); see attention_sink_prefill.cu.
 int hb_attention_sink_prefill_supported(int n_heads, int n_kv_heads, int head_dim, int v_dim);
@@ -188,9 +188,25 @@ int hb_attention_pool_prefill(const void* q, long long q_stride, const void* k_c
 // Matrix memory with a fixed decay per head (decay_memory.cu).  proj rows: [q heads*d | k heads*d | v heads*dv | ...] float32;
 // state per slot: S [heads][d][dv]; out [tokens][heads*dv] float32; act 1: silu on q, k and v
 int hb_decay_memory(const float* proj, long long ldp, const float* decay, float* state, long long state_stride, const int* state_slots,
-                    const int* seq_start, float* out, long long ldo, int n_seqs, int n_heads, int d, int dv, int act, void* stream);
+                    const int* seq_start, float* out, long long ldo, int n_seqs, int n_heads, int d, int dv, int act, const float* table,
+                    int rot, float k_scale, void* stream);
 int hb_gated_norm(const float* o, long long ldi, const float* gate, long long ldg, const float* w, float eps, float out_scale, void* out,
-                  int out_dtype, long long ldo, int n_rows, int n, void* stream);
+                  int out_dtype, long long ldo, int n_rows, int n, int group, int gate_kind, void* stream);
+// Layer norm with weight and bias: alone (optionally over gathered rows), and on a sublayer's output on its way into the
+// residual stream (of one output, or of the weighted sum sa * y + sb * y2), with a copy of the new rows in another dtype
+// (layer_norm.cu)
+int hb_layernorm(const float* x, long long ldx, const float* w, const float* b, float eps, void* out, int out_dtype, long long ldo,
+                 const int* rows, int n_rows, int n, void* stream);
+int hb_layernorm_add(const float* y, long long ldy, const float* y2, long long ldy2, float sa, float sb, const float* w, const float* b,
+                     float eps, float* x, long long ldx, void* copy, int copy_dtype, long long ldc, int n_rows, int n, void* stream);
+int hb_convert(const float* x, void* out, int out_dtype, long long n, void* stream);
+// Attention over one cached latent per token (latent_attention.cu): the cache rows, and the per-head products around it
+int hb_latent_prepare(const float* proj, long long ldp, int n_heads, int d, int dr, int rank, int down_at, const float* c_weight, float eps,
+                      const float* table, int rot, void* q_out, int q_dtype, long long ldq, void* k_cache, void* v_cache, int cache_dtype,
+                      const int* page_table, int pt_width, const int* tok_seq, const int* positions, int n_tokens, int n_pages, int append,
+                      int* status, void* stream);
+int hb_head_linear(const float* in, long long ldi, long long in_head, const void* w, int w_dtype, void* out, int out_dtype, long long ldo,
+                   long long out_head, const float* gate, long long ldg, int n_tokens, int n_heads, int n_in, int n_out, void* stream);
 // Short causal convolution with bias, activation and state; selective state-space scan (selective_scan.cu)
 int hb_conv_act(const float* x, long long ldx, const float* conv_w, const float* conv_b, int taps, float* state, long long state_stride,
                 const int* state_slots, const int* seq_start, void* out, int out_dtype, long long ldo, int n_seqs, int max_new, int C,

@@ -24,7 +24,8 @@
 template <typename TP, typename TQ, typename TC>
 __global__ void __launch_bounds__(QP_THREADS)
 qkv_prepare_kernel(const TP* __restrict__ proj, long long ldp, const float* __restrict__ bias, const float2* __restrict__ table,
-                   int rot, int nh, int nkv, int hd, int vd, int unit_norm, float eps, TQ* __restrict__ q_out, long long ldq,
+                   int rot, int nh, int nkv, int hd, int vd, int unit_norm, const float* __restrict__ q_norm_w,
+                   const float* __restrict__ k_norm_w, float eps, TQ* __restrict__ q_out, long long ldq,
                    TC* __restrict__ k_cache, TC* __restrict__ v_cache, const int* __restrict__ page_table, int pt_width,
                    const int* __restrict__ tok_seq, const int* __restrict__ positions, int n_pages, int append,
                    const float* __restrict__ v_lambda, float* __restrict__ v_first, int v_mode, int* status) {
@@ -51,6 +52,16 @@ qkv_prepare_kernel(const TP* __restrict__ proj, long long ldp, const float* __re
         const TP* row = proj + (size_t)t * ldp + col0;
         for (int d = tid; d < hd; d += QP_THREADS) xs[d] = to_f32(row[d]) + (bias ? bias[col0 + d] : 0.0f);
         __syncthreads();
+        if (unit_norm == 2) {
+            // the head divided by its root mean square and multiplied by a weight BEFORE the rotation
+            const float* nw = is_q ? q_norm_w : k_norm_w;
+            float s0 = 0.0f;
+            for (int d = tid; d < hd; d += QP_THREADS) s0 = fmaf(xs[d], xs[d], s0);
+            s0 = block_sum(s0, scratch);
+            const float inv0 = 1.0f / sqrtf(s0 / (float)hd + eps);
+            for (int d = tid; d < hd; d += QP_THREADS) xs[d] = xs[d] * inv0 * nw[d];
+            __syncthreads();
+        }
         const int half = rot >> 1;
         float ss = 0.0f;
         for (int d = tid; d < hd; d += QP_THREADS) {
@@ -66,7 +77,7 @@ qkv_prepare_kernel(const TP* __restrict__ proj, long long ldp, const float* __re
         }
         // second pass with the factor (recomputes the rotation: xs still holds the inputs)
         float inv = 1.0f;
-        if (unit_norm) {
+        if (unit_norm == 1) {
             ss = block_sum(ss, scratch);
             inv = 1.0f / sqrtf(ss / (float)hd + eps);
         }
@@ -99,8 +110,8 @@ qkv_prepare_kernel(const TP* __restrict__ proj, long long ldp, const float* __re
 }
 
 extern "C" int hb_qkv_prepare(const void* proj, int proj_dtype, long long ldp, const float* bias, const float* table, int rot,
-                              int n_heads, int n_kv_heads, int head_dim, int v_dim, int unit_norm, float eps, void* q_out,
-                              int q_dtype, long long ldq, void* k_cache, void* v_cache, int cache_dtype, const int* page_table,
+                              int n_heads, int n_kv_heads, int head_dim, int v_dim, int unit_norm, const float* q_norm_w,
+                              const float* k_norm_w, float eps, void* q_out, int q_dtype, long long ldq, void* k_cache, void* v_cache, int cache_dtype, const int* page_table,
                               int pt_width, const int* tok_seq, const int* positions, int n_tokens, int n_pages, int append,
                               const float* v_lambda, float* v_first, int v_mode, int* status, void* stream) {
     if (n_tokens == 0) return 0;
@@ -108,6 +119,8 @@ extern "C" int hb_qkv_prepare(const void* proj, int proj_dtype, long long ldp, c
     HB_REQUIRE(head_dim <= QP_MAX_HD, "qkv_prepare: head size %d is larger than %d", head_dim, QP_MAX_HD);
     HB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= head_dim, "qkv_prepare: %d rotated dimensions of %d", rot, head_dim);
     HB_REQUIRE(rot == 0 || table != nullptr, "qkv_prepare: no rotation table");
+    HB_REQUIRE(unit_norm >= 0 && unit_norm <= 2 && (unit_norm != 2 || (q_norm_w != nullptr && k_norm_w != nullptr)),
+               "qkv_prepare: norm mode %d (0 none, 1 unit norm behind the rotation, 2 weighted norm in front of it)", unit_norm);
     HB_REQUIRE(v_mode >= 0 && v_mode <= 2 && (v_mode == 0 || v_first != nullptr) && (v_mode != 2 || v_lambda != nullptr),
                "qkv_prepare: value mixing needs its buffers");
     HB_REQUIRE(n_heads + 2 * n_kv_heads <= 65535, "qkv_prepare: too many heads");
@@ -117,7 +130,7 @@ extern "C" int hb_qkv_prepare(const void* proj, int proj_dtype, long long ldp, c
     cudaStream_t s = (cudaStream_t)stream;
 #define HB_QP_LAUNCH(TP, TQ)                                                                                                   \
     hb_launch(qkv_prepare_kernel<TP, TQ, TQ>, dim3(grid), dim3(QP_THREADS), 0, s, (const TP*)proj, ldp, bias, (const float2*)table, rot,  \
-              n_heads, n_kv_heads, head_dim, v_dim, unit_norm, eps, (TQ*)q_out, ldq, (TQ*)k_cache, (TQ*)v_cache, page_table,       \
+              n_heads, n_kv_heads, head_dim, v_dim, unit_norm, q_norm_w, k_norm_w, eps, (TQ*)q_out, ldq, (TQ*)k_cache, (TQ*)v_cache, page_table,       \
               pt_width, tok_seq, positions, n_pages, append, v_lambda, v_first, v_mode, status)
     if (proj_dtype == HB_F32 && q_dtype == HB_F32) HB_QP_LAUNCH(float, float);
     else if (proj_dtype == HB_F32 && q_dtype == HB_BF16) HB_QP_LAUNCH(float, bf16);
@@ -129,7 +142,7 @@ extern "C" int hb_qkv_prepare(const void* proj, int proj_dtype, long long ldp, c
 
 // ---------------------------------------------------------------------------------------------
 #define AS_THREADS 128
-#define AS_MAX_HD 512
+#define AS_MAX_HD 1024
 #define AS_MAX_ACC 16         // value columns per thread: (value heads served) * v_dim <= 128 * 16
 
 template <typename TQ, typename TC>
@@ -253,10 +266,11 @@ extern "C" int hb_attention_sink(const void* q, int q_dtype, long long ldq, cons
 template <typename TO>
 __global__ void __launch_bounds__(256)
 head_mix_kernel(const float* __restrict__ partial, const float* __restrict__ mix, TO* __restrict__ out, long long ldo, int nh,
-                int nkv, int vd, int n_val, int ones) {
+                int nkv, int vd, int n_val, int ones, const float* __restrict__ gate, long long ldg) {
     pdl_trigger();
     pdl_wait();
     partial = pdl_fresh(partial);
+    gate = pdl_fresh(gate);
     const int t = blockIdx.x;
     const float* pr = partial + (size_t)t * nh * n_val * vd;
     TO* o = out + (size_t)t * ldo;
@@ -271,13 +285,14 @@ head_mix_kernel(const float* __restrict__ partial, const float* __restrict__ mix
         } else {
             a = pr[(size_t)h * n_val * vd + d];
         }
+        if (gate != nullptr) a *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h]));     // one gate per (token, head)
         o[e] = from_f32<TO>(a);
     }
     for (int e = threadIdx.x; e < ones; e += blockDim.x) o[nh * vd + e] = from_f32<TO>(e == 0 ? 1.0f : 0.0f);
 }
 
 extern "C" int hb_head_mix(const float* partial, const float* mix, void* out, int out_dtype, long long ldo, int n_tokens,
-                           int n_heads, int n_kv_heads, int v_dim, int n_val, int ones, void* stream) {
+                           int n_heads, int n_kv_heads, int v_dim, int n_val, int ones, const float* gate, long long ldg, void* stream) {
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && v_dim > 0 && ones >= 0, "head_mix: bad sizes");
     HB_REQUIRE(n_val == 1 || n_val == n_kv_heads, "head_mix: partial results hold %d value heads, 1 or %d expected", n_val, n_kv_heads);
@@ -285,9 +300,9 @@ extern "C" int hb_head_mix(const float* partial, const float* mix, void* out, in
     HB_REQUIRE(ldo >= (long long)n_heads * v_dim + ones, "head_mix: output rows are too short");
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == HB_BF16)
-        hb_launch(head_mix_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, partial, mix, (bf16*)out, ldo, n_heads, n_kv_heads, v_dim, n_val, ones);
+        hb_launch(head_mix_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, partial, mix, (bf16*)out, ldo, n_heads, n_kv_heads, v_dim, n_val, ones, gate, ldg);
     else if (out_dtype == HB_F32)
-        hb_launch(head_mix_kernel<float>, dim3(n_tokens), dim3(256), 0, s, partial, mix, (float*)out, ldo, n_heads, n_kv_heads, v_dim, n_val, ones);
+        hb_launch(head_mix_kernel<float>, dim3(n_tokens), dim3(256), 0, s, partial, mix, (float*)out, ldo, n_heads, n_kv_heads, v_dim, n_val, ones, gate, ldg);
     else return hb_fail("head_mix: unsupported output dtype %d", out_dtype);
     return hb_check_launch("head_mix");
 }
@@ -732,13 +747,15 @@ extern "C" int hb_attention_heads(const void* q, int q_dtype, long long ldq, con
 template <typename TO>
 __global__ void __launch_bounds__(256)
 head_mix_splits_kernel(const float* __restrict__ partial, const float* __restrict__ ml, const float* __restrict__ mix,
-                       TO* __restrict__ out, long long ldo, int nh, int nkv, int vd, int splits, int ones) {
+                       TO* __restrict__ out, long long ldo, int nh, int nkv, int vd, int splits, int ones,
+                       const float* __restrict__ gate, long long ldg) {
     // one block per (token, value head c, run of HM_COLS columns of c): first the splits of every head are combined
     // for these columns (shared memory [nh][HM_COLS]), then the heads that use c mix them
     pdl_trigger();
     pdl_wait();
     partial = pdl_fresh(partial);
     ml = pdl_fresh(ml);
+    gate = pdl_fresh(gate);
     extern __shared__ float hm_smem[];
     float* wts = hm_smem;                               // [nh][splits]: w_gs / (sum_s w_gs l_gs)
     float* comb = hm_smem + nh * splits;                // [nh][HM_COLS]
@@ -774,6 +791,7 @@ head_mix_splits_kernel(const float* __restrict__ partial, const float* __restric
         } else {
             a = comb[h * HM_COLS + d];
         }
+        if (gate != nullptr) a *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h]));
         o[h * vd + d_begin + d] = from_f32<TO>(a);
     }
     if (c == 0 && blockIdx.z == 0)
@@ -781,7 +799,8 @@ head_mix_splits_kernel(const float* __restrict__ partial, const float* __restric
 }
 
 extern "C" int hb_head_mix_splits(const float* partial, const float* ml, const float* mix, void* out, int out_dtype, long long ldo,
-                                  int n_tokens, int n_heads, int n_kv_heads, int v_dim, int splits, int ones, void* stream) {
+                                  int n_tokens, int n_heads, int n_kv_heads, int v_dim, int splits, int ones, const float* gate,
+                                  long long ldg, void* stream) {
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && v_dim > 0 && ones >= 0 && splits >= 1, "head_mix: bad sizes");
     HB_REQUIRE(ldo >= (long long)n_heads * v_dim + ones, "head_mix: output rows are too short");
@@ -790,9 +809,9 @@ extern "C" int hb_head_mix_splits(const float* partial, const float* ml, const f
     HB_REQUIRE(smem <= 48 * 1024 && n_kv_heads <= 65535, "head_mix: too many heads times (splits + value size)");
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == HB_BF16)
-        hb_launch(head_mix_splits_kernel<bf16>, dim3(n_tokens, n_kv_heads, (v_dim + HM_COLS - 1) / HM_COLS), dim3(256), smem, s, partial, ml, mix, (bf16*)out, ldo, n_heads, n_kv_heads, v_dim, splits, ones);
+        hb_launch(head_mix_splits_kernel<bf16>, dim3(n_tokens, n_kv_heads, (v_dim + HM_COLS - 1) / HM_COLS), dim3(256), smem, s, partial, ml, mix, (bf16*)out, ldo, n_heads, n_kv_heads, v_dim, splits, ones, gate, ldg);
     else if (out_dtype == HB_F32)
-        hb_launch(head_mix_splits_kernel<float>, dim3(n_tokens, n_kv_heads, (v_dim + HM_COLS - 1) / HM_COLS), dim3(256), smem, s, partial, ml, mix, (float*)out, ldo, n_heads, n_kv_heads, v_dim, splits, ones);
+        hb_launch(head_mix_splits_kernel<float>, dim3(n_tokens, n_kv_heads, (v_dim + HM_COLS - 1) / HM_COLS), dim3(256), smem, s, partial, ml, mix, (float*)out, ldo, n_heads, n_kv_heads, v_dim, splits, ones, gate, ldg);
     else return hb_fail("head_mix: unsupported output dtype %d", out_dtype);
     return hb_check_launch("head_mix_splits");
 }

@@ -1,6 +1,8 @@
 // A matrix memory with a fixed decay per head (linear attention with exponential forgetting):
 //   S_t = decay_h S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t        (S: head size x value size, 32-bit)
-// with q, k, v = act(projections), act = silu or nothing.  The state is carried per sequence.
+// with q, k, v = act(projections), act = silu or nothing; optionally q and k are then turned by the step's
+// rotation table (pairs (i, i + rot/2) of the first rot dimensions of every head) and k is multiplied by a
+// constant.  The state is carried per sequence.
 //
 // decay_memory: DM_CHUNK tokens at a time.  Within a chunk that starts from S0 (tokens j, s = 0 ..):
 //   o_j = decay^(j+1) S0^T q_j + sum_{s <= j} decay^(j-s) (q_j . k_s) v_s
@@ -9,8 +11,9 @@
 // itself (decode steps).  Only non-negative powers of the decay appear, nothing is divided.  One
 // block per (slice of DM_COLS value columns, head, sequence), everything in 32-bit FP32-pipe code.
 //
-// gated_norm: out = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) * out_scale over each row (all
-// heads together), rounded once for the output product.
+// gated_norm: out = o / sqrt(mean(o^2) + eps) * w * f(gate) * out_scale, the mean taken over each row (all
+// heads together) or over each run of `group` values of it (a head at a time); w may be absent, f is
+// sigmoid or silu; rounded once for the output product.
 #include "api.h"
 #include "common.cuh"
 
@@ -30,7 +33,8 @@ __device__ __forceinline__ float dm_act(float z, int act) { return act == 1 ? z 
 __global__ void __launch_bounds__(DM_THREADS)
 decay_memory_kernel(const float* __restrict__ proj, long long ldp, const float* __restrict__ decay, float* __restrict__ state,
                     long long state_stride, const int* __restrict__ state_slots, const int* __restrict__ seq_start,
-                    float* __restrict__ out, long long ldo, int H, int d, int dv, int act) {
+                    float* __restrict__ out, long long ldo, int H, int d, int dv, int act, const float2* __restrict__ table, int rot,
+                    float k_scale) {
     pdl_trigger();
     extern __shared__ float dm_smem[];
     float* Qs = dm_smem;
@@ -49,6 +53,7 @@ decay_memory_kernel(const float* __restrict__ proj, long long ldp, const float* 
     pdl_wait();
     proj = pdl_fresh(proj);
     state = pdl_fresh(state);
+    table = pdl_fresh(table);
     float* S = state + (size_t)state_slots[b] * state_stride + (size_t)h * d * dv;
     for (int i = grp; i < d; i += DM_GROUPS) Ss[i * DM_COLS + lane] = live ? S[(size_t)i * dv + col] : 0.0f;
     const long long qo = (long long)h * d, ko = (long long)H * d + (long long)h * d, vo = (long long)2 * H * d + (long long)h * dv;
@@ -105,6 +110,28 @@ decay_memory_kernel(const float* __restrict__ proj, long long ldp, const float* 
                 Vs[i] = (c0 + c < dv) ? dm_act(proj[(size_t)(start + base + j) * ldp + vo + c0 + c], act) : 0.0f;
             }
         }
+        if (rot > 0 || k_scale != 1.0f) {
+            // the staged queries and keys turned in place by their tokens' angles; the keys scaled
+            __syncthreads();
+            const int half = rot >> 1;
+            for (int i = tid; i < n * half; i += DM_THREADS) {
+                const int j = i / half, c = i - j * half;
+                const float2 cs = table[(size_t)(start + base + j) * half + c];
+                float* qr = Qs + j * (d + 1);
+                float* kr = Ks + j * (d + 1);
+                float y1, y2;
+                rope_pair(qr[c], qr[c + half], cs.x, cs.y, y1, y2);
+                qr[c] = y1;
+                qr[c + half] = y2;
+                rope_pair(kr[c], kr[c + half], cs.x, cs.y, y1, y2);
+                kr[c] = y1;
+                kr[c + half] = y2;
+            }
+            if (k_scale != 1.0f) {
+                __syncthreads();
+                for (int i = tid; i < n * d; i += DM_THREADS) Ks[(i / d) * (d + 1) + i % d] *= k_scale;
+            }
+        }
         __syncthreads();
         // a[j][s] = decay^(j-s) q_j . k_s for s <= j
         for (int i = tid; i < n * n; i += DM_THREADS) {
@@ -145,12 +172,13 @@ decay_memory_kernel(const float* __restrict__ proj, long long ldp, const float* 
 
 extern "C" int hb_decay_memory(const float* proj, long long ldp, const float* decay, float* state, long long state_stride,
                                const int* state_slots, const int* seq_start, float* out, long long ldo, int n_seqs, int n_heads,
-                               int d, int dv, int act, void* stream) {
+                               int d, int dv, int act, const float* table, int rot, float k_scale, void* stream) {
     if (n_seqs == 0) return 0;
     HB_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_heads > 0 && n_heads <= 65535 && d > 0 && dv > 0, "decay_memory: bad sizes");
     HB_REQUIRE(d <= DM_MAX_DIM, "decay_memory: head size %d (up to %d is built)", d, DM_MAX_DIM);
     HB_REQUIRE(ldp >= (long long)n_heads * (2 * d + dv) && state_stride >= (long long)n_heads * d * dv, "decay_memory: rows are too short");
     HB_REQUIRE(act == 0 || act == 1, "decay_memory: activation %d (0 none, 1 silu)", act);
+    HB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d && (rot == 0 || table != nullptr), "decay_memory: %d rotated dimensions of %d", rot, d);
     static bool done[HB_MAX_DEVICES] = {};
     const int slot = hb_device_slot();
     if (!done[slot]) {
@@ -160,15 +188,18 @@ extern "C" int hb_decay_memory(const float* proj, long long ldp, const float* de
     }
     dim3 grid((dv + DM_COLS - 1) / DM_COLS, n_heads, n_seqs);
     hb_launch(decay_memory_kernel, dim3(grid), dim3(DM_THREADS), dm_smem_bytes(d), (cudaStream_t)stream, proj, ldp, decay, state, state_stride,
-              state_slots, seq_start, out, ldo, n_heads, d, dv, act);
+              state_slots, seq_start, out, ldo, n_heads, d, dv, act, (const float2*)table, rot, k_scale);
     return hb_check_launch("decay_memory");
 }
 
 // ------------------------------------------------------------------------------------------------ gated_norm
+__device__ __forceinline__ float gn_gate(float z, int kind) { return kind == 1 ? z / (1.0f + expf(-z)) : 1.0f / (1.0f + expf(-z)); }
+
 template <typename TO>
 __global__ void __launch_bounds__(256)
 gated_norm_kernel(const float* __restrict__ o, long long ldi, const float* __restrict__ gate, long long ldg,
-                  const float* __restrict__ w, float eps, float out_scale, TO* __restrict__ out, long long ldo, int n) {
+                  const float* __restrict__ w, float eps, float out_scale, TO* __restrict__ out, long long ldo, int n, int group,
+                  int gate_kind) {
     pdl_trigger();
     pdl_wait();
     o = pdl_fresh(o);
@@ -176,26 +207,46 @@ gated_norm_kernel(const float* __restrict__ o, long long ldi, const float* __res
     __shared__ float scratch[33];
     const int t = blockIdx.x;
     const float* r = o + (size_t)t * ldi;
+    if (group < n) {
+        // a warp per run of `group` values
+        const int lane = threadIdx.x & 31;
+        for (int g = threadIdx.x >> 5; g * group < n; g += 8) {
+            const float* rg = r + (size_t)g * group;
+            float ss = 0.0f;
+            for (int i = lane; i < group; i += 32) ss = fmaf(rg[i], rg[i], ss);
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)group + eps);
+            for (int i = lane; i < group; i += 32) {
+                const int e = g * group + i;
+                float v = rg[i] * inv * (w ? w[e] : 1.0f);
+                if (gate != nullptr) v *= gn_gate(gate[(size_t)t * ldg + e], gate_kind);
+                out[(size_t)t * ldo + e] = from_f32<TO>(v * out_scale);
+            }
+        }
+        return;
+    }
     float ss = 0.0f;
     for (int i = threadIdx.x; i < n; i += 256) ss = fmaf(r[i], r[i], ss);
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)n + eps);
     for (int i = threadIdx.x; i < n; i += 256) {
-        float v = r[i] * inv * w[i];
-        if (gate != nullptr) v *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + i]));
+        float v = r[i] * inv * (w ? w[i] : 1.0f);
+        if (gate != nullptr) v *= gn_gate(gate[(size_t)t * ldg + i], gate_kind);
         out[(size_t)t * ldo + i] = from_f32<TO>(v * out_scale);
     }
 }
 
 extern "C" int hb_gated_norm(const float* o, long long ldi, const float* gate, long long ldg, const float* w, float eps, float out_scale,
-                             void* out, int out_dtype, long long ldo, int n_rows, int n, void* stream) {
+                             void* out, int out_dtype, long long ldo, int n_rows, int n, int group, int gate_kind, void* stream) {
     if (n_rows == 0) return 0;
     HB_REQUIRE(n_rows > 0 && n > 0 && ldi >= n && ldo >= n, "gated_norm: bad sizes");
+    HB_REQUIRE(group > 0 && n % group == 0, "gated_norm: runs of %d values do not divide a row of %d", group, n);
+    HB_REQUIRE(gate_kind == 0 || gate_kind == 1, "gated_norm: gate %d (0 sigmoid, 1 silu)", gate_kind);
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == HB_BF16)
-        hb_launch(gated_norm_kernel<bf16>, dim3(n_rows), dim3(256), 0, s, o, ldi, gate, ldg, w, eps, out_scale, (bf16*)out, ldo, n);
+        hb_launch(gated_norm_kernel<bf16>, dim3(n_rows), dim3(256), 0, s, o, ldi, gate, ldg, w, eps, out_scale, (bf16*)out, ldo, n, group, gate_kind);
     else if (out_dtype == HB_F32)
-        hb_launch(gated_norm_kernel<float>, dim3(n_rows), dim3(256), 0, s, o, ldi, gate, ldg, w, eps, out_scale, (float*)out, ldo, n);
+        hb_launch(gated_norm_kernel<float>, dim3(n_rows), dim3(256), 0, s, o, ldi, gate, ldg, w, eps, out_scale, (float*)out, ldo, n, group, gate_kind);
     else return hb_fail("gated_norm: unsupported output dtype %d", out_dtype);
     return hb_check_launch("gated_norm");
 }

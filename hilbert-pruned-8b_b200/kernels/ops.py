@@ -33,18 +33,18 @@ _SIGNATURES = {
     "hb_short_conv": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll,
                       _c_int, _c_int, _c_int, _c_ptr],
     "hb_relu2": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
-    "hb_qkv_prepare": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr,
+    "hb_qkv_prepare": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr,
                        _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                        _c_ptr, _c_int, _c_ptr, _c_ptr],
     "hb_attention_sink": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                           _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
-    "hb_head_mix": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_head_mix": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ll, _c_ptr],
     "hb_attention_heads": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                            _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
                            _c_ptr],
     "hb_attention_sink_prefill": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                   _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
-    "hb_head_mix_splits": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_head_mix_splits": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ll, _c_ptr],
     "hb_mlstm_scan": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                       _c_int, _c_int, _c_ptr],
     "hb_mlstm_chunks": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
@@ -88,8 +88,17 @@ _SIGNATURES = {
                           _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_attention_pool_prefill": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ll,
                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
-    "hb_decay_memory": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
-    "hb_gated_norm": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
+    "hb_decay_memory": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
+                        _c_int, _c_float, _c_ptr],
+    "hb_gated_norm": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_layernorm": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_ptr],
+    "hb_layernorm_add": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_float, _c_float, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ll, _c_ptr, _c_int, _c_ll,
+                         _c_int, _c_int, _c_ptr],
+    "hb_convert": [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr],
+    "hb_latent_prepare": [_c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_int, _c_ll,
+                          _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_head_linear": [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_int, _c_ptr, _c_int, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int,
+                       _c_ptr],
     "hb_conv_act": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int,
                     _c_int, _c_ptr],
     "hb_selective_scan": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr,
@@ -493,13 +502,18 @@ class Ops:
 
     # ------------------------------------------------------------------ attention with kept first tokens and mixed heads
     def qkv_prepare(self, proj, bias, table, rot: int, heads: int, kv_heads: int, head_dim: int, v_dim: int, unit_norm: bool,
-                    eps: float, q_out, cache, step, append: bool, v_lambda=None, v_first=None, v_mode: int = 0) -> None:
+                    eps: float, q_out, cache, step, append: bool, v_lambda=None, v_first=None, v_mode: int = 0,
+                    norm_weights=None) -> None:
         """From a step's projections ``[q | k | v]``: biases added, queries and keys turned by ``table`` and (``unit_norm``)
-        divided by their root mean square per head; queries to ``q_out``, keys and values into the cache.  ``v_mode`` 1 also
+        divided by their root mean square per head; queries to ``q_out``, keys and values into the cache.  ``norm_weights``
+        ``(wq, wk)`` (float32 ``[head_dim]`` each): instead, every head of q and of k is divided by its root mean square and
+        multiplied by its weight BEFORE the rotation.  ``v_mode`` 1 also
         keeps the values in ``v_first`` (float32 ``[tokens, kv_heads * v_dim]``), 2 mixes them with it:
         ``v <- (1 - v_lambda) v + v_lambda v_first``."""
         self._dev(proj, bias, table, q_out, cache.k, cache.v, v_lambda, v_first)
         T = proj.shape[0]
+        if norm_weights is not None and unit_norm:
+            raise KernelError("qkv_prepare: one norm of queries and keys at a time")
         width = heads * head_dim + kv_heads * (head_dim + v_dim)
         if proj.shape[1] < width or tuple(q_out.shape) != (T, heads * head_dim):
             raise KernelError("qkv_prepare: shapes do not agree")
@@ -513,7 +527,10 @@ class Ops:
         pt = step.page_tables[cache.group]
         self._call("hb_qkv_prepare", proj.data_ptr(), _code(proj), _rows(proj, "projections"),
                    self._f32_vec(bias, width, "projection bias") if bias is not None else None,
-                   table.data_ptr() if rot else None, rot, heads, kv_heads, head_dim, v_dim, 1 if unit_norm else 0, float(eps),
+                   table.data_ptr() if rot else None, rot, heads, kv_heads, head_dim, v_dim,
+                   2 if norm_weights is not None else 1 if unit_norm else 0,
+                   self._f32_vec(norm_weights[0], head_dim, "query norm weight") if norm_weights is not None else None,
+                   self._f32_vec(norm_weights[1], head_dim, "key norm weight") if norm_weights is not None else None, float(eps),
                    q_out.data_ptr(), _code(q_out), _rows(q_out, "queries"), cache.k.data_ptr(), cache.v.data_ptr(), _code(cache.k),
                    pt.data_ptr(), pt.shape[1], step.tok_seq.data_ptr(), step.positions.data_ptr(), T, cache.k.shape[0],
                    1 if append else 0, self._f32_vec(v_lambda, 1, "value mix") if v_lambda is not None else None,
@@ -539,15 +556,25 @@ class Ops:
                    int(keep_first), 1 if all_values else 0, cache.k.shape[0], self.status.data_ptr(), self._stream())
         self.launches += 1
 
-    def head_mix(self, partial, mix, out, heads: int, kv_heads: int, v_dim: int, n_val: int, ones: int = 0) -> None:
+    def _head_gate(self, gate, T: int, heads: int):
+        """Pointer and row stride of a per-(token, head) gate, float32 ``[tokens, heads]`` with contiguous rows, or (None, 0)."""
+        if gate is None:
+            return None, 0
+        if gate.dtype != torch.float32 or tuple(gate.shape) != (T, heads):
+            raise KernelError("head gate: float32 [tokens, heads] expected")
+        return gate.data_ptr(), _rows(gate, "head gate")
+
+    def head_mix(self, partial, mix, out, heads: int, kv_heads: int, v_dim: int, n_val: int, ones: int = 0, gate=None) -> None:
         """``out[t, h] = sum_g mix[h, g] partial[t, g, kv(h)]`` (``mix`` None: the head's own); ``ones`` more columns
-        (a one, then zeros) follow, through which the next product adds a bias stored as a column of its weight."""
-        self._dev(partial, mix, out)
+        (a one, then zeros) follow, through which the next product adds a bias stored as a column of its weight.  ``gate``
+        float32 ``[tokens, heads]``: head h's result is multiplied by ``sigmoid(gate[t, h])``."""
+        self._dev(partial, mix, out, gate)
         T = out.shape[0]
         if out.shape[1] != heads * v_dim + ones or partial.numel() != T * heads * n_val * v_dim:
             raise KernelError("head_mix: shapes do not agree")
         self._call("hb_head_mix", partial.data_ptr(), self._f32_vec(mix, heads * heads, "head mix") if mix is not None else None,
-                   out.data_ptr(), _code(out), _rows(out, "head_mix output"), T, heads, kv_heads, v_dim, n_val, ones, self._stream())
+                   out.data_ptr(), _code(out), _rows(out, "head_mix output"), T, heads, kv_heads, v_dim, n_val, ones,
+                   *self._head_gate(gate, T, heads), self._stream())
         self.launches += 1
 
     SINK_PREFILL_FROM = 16          # steps whose longest portion has at least so many tokens run the flash-style kernel
@@ -630,16 +657,16 @@ class Ops:
                    cache.k.shape[0], 1 if self.use_mma_attention else 0, self.status.data_ptr(), self._stream())
         self.launches += 1
 
-    def head_mix_splits(self, partial, ml, mix, out, heads: int, kv_heads: int, v_dim: int, splits: int, ones: int = 0) -> None:
+    def head_mix_splits(self, partial, ml, mix, out, heads: int, kv_heads: int, v_dim: int, splits: int, ones: int = 0, gate=None) -> None:
         """Combines the key splits of ``attention_heads`` and mixes the heads (``mix`` None: each head its own).  ``ml`` None:
         one split, normalised already (``partial`` is then ``[tokens, heads, kv_heads, v_dim]``)."""
-        self._dev(partial, ml, mix, out)
+        self._dev(partial, ml, mix, out, gate)
         T = out.shape[0]
         if out.shape[1] != heads * v_dim + ones:
             raise KernelError("head_mix_splits: shapes do not agree")
         self._call("hb_head_mix_splits", partial.data_ptr(), ml.data_ptr() if ml is not None else None,
                    self._f32_vec(mix, heads * heads, "head mix") if mix is not None else None, out.data_ptr(), _code(out),
-                   _rows(out, "head_mix output"), T, heads, kv_heads, v_dim, splits, ones, self._stream())
+                   _rows(out, "head_mix output"), T, heads, kv_heads, v_dim, splits, ones, *self._head_gate(gate, T, heads), self._stream())
         self.launches += 1
 
     # ------------------------------------------------------------------ matrix memory (mLSTM)
@@ -1120,11 +1147,15 @@ class Ops:
     # ------------------------------------------------------------------ matrix memory with a fixed decay
     ACTIVATIONS = {None: 0, "none": 0, "silu": 1}
 
-    def decay_memory(self, proj, decay, state, step, out, heads: int, d: int, dv: int, activation="silu") -> None:
+    def decay_memory(self, proj, decay, state, step, out, heads: int, d: int, dv: int, activation="silu", table=None, rot: int = 0,
+                     k_scale: float = 1.0) -> None:
         """``S <- decay[h] S + k v^T; o = S^T q`` per head over a step's tokens, sequence by sequence, with q, k, v the
         activation of the float32 projections ``[q | k | v | ...]``; ``state`` float32 ``[slots, heads * d * dv]``, ``out``
-        float32 ``[tokens, heads * dv]``."""
-        self._dev(proj, decay, state, out)
+        float32 ``[tokens, heads * dv]``.  With ``table`` (``[tokens, rot / 2, 2]`` cosines and sines) the first ``rot``
+        dimensions of every head of q and k are turned first; ``k_scale`` multiplies k after that."""
+        self._dev(proj, decay, state, out, table)
+        if rot and (table is None or table.dtype != torch.float32 or not table.is_contiguous() or tuple(table.shape[:2]) != (proj.shape[0], rot // 2)):
+            raise KernelError("decay_memory: rotary table does not match the tokens")
         T = proj.shape[0]
         if proj.dtype != torch.float32 or out.dtype != torch.float32 or tuple(out.shape) != (T, heads * dv):
             raise KernelError("decay_memory: float32 projections and float32 [tokens, heads * dv] output expected")
@@ -1132,18 +1163,100 @@ class Ops:
             raise KernelError("decay_memory: state must be float32 [slots, heads * d * dv]")
         self._call("hb_decay_memory", proj.data_ptr(), _rows(proj, "projections"), self._f32_vec(decay, heads, "decay"), state.data_ptr(),
                    state.stride(0), step.state_slots.data_ptr(), step.seq_start.data_ptr(), out.data_ptr(), _rows(out, "output"),
-                   step.num_seqs, heads, d, dv, self.ACTIVATIONS[activation], self._stream())
+                   step.num_seqs, heads, d, dv, self.ACTIVATIONS[activation], table.data_ptr() if rot else None, int(rot), float(k_scale),
+                   self._stream())
         self.launches += 1
 
-    def gated_norm(self, o, gate, weight, eps: float, out, out_scale: float = 1.0) -> None:
-        """``out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate) * out_scale`` over whole rows (``gate`` may be None)."""
+    GATES = {"sigmoid": 0, "silu": 1}
+
+    def gated_norm(self, o, gate, weight, eps: float, out, out_scale: float = 1.0, group: Optional[int] = None, gate_kind: str = "sigmoid") -> None:
+        """``out = o / sqrt(mean(o^2) + eps) * weight * f(gate) * out_scale``; the mean over whole rows, or with ``group`` over
+        every run of that many values of a row; ``gate`` and ``weight`` may be None; f is sigmoid or silu."""
         self._dev(o, gate, weight, out)
         T, n = o.shape
+        if gate_kind not in self.GATES:
+            raise KernelError(f"gated_norm: gate {gate_kind!r} ({', '.join(self.GATES)})")
         if o.dtype != torch.float32 or tuple(out.shape) != (T, n) or (gate is not None and (gate.dtype != torch.float32 or tuple(gate.shape) != (T, n))):
             raise KernelError("gated_norm: float32 [tokens, n] input and gate expected")
         self._call("hb_gated_norm", o.data_ptr(), _rows(o, "gated_norm input"), gate.data_ptr() if gate is not None else None,
-                   _rows(gate, "gate") if gate is not None else 0, self._f32_vec(weight, n, "norm weight"), float(eps), float(out_scale),
-                   out.data_ptr(), _code(out), _rows(out, "gated_norm output"), T, n, self._stream())
+                   _rows(gate, "gate") if gate is not None else 0, self._f32_vec(weight, n, "norm weight") if weight is not None else None,
+                   float(eps), float(out_scale), out.data_ptr(), _code(out), _rows(out, "gated_norm output"), T, n,
+                   int(group) if group else n, self.GATES[gate_kind], self._stream())
+        self.launches += 1
+
+    # ------------------------------------------------------------------ layer norm (alone, and on a sublayer's output)
+    def layernorm(self, x, weight, bias, eps: float, out, rows=None) -> None:
+        """``out[i] = (x[r] - mean) / sqrt(var + eps) * weight + bias`` with ``r = rows[i]`` (``rows`` None: every row), 32-bit."""
+        self._dev(x, weight, bias, out, rows)
+        n = x.shape[1]
+        if x.dtype != torch.float32 or out.shape[1] != n or (rows is None and out.shape[0] != x.shape[0]):
+            raise KernelError("layernorm: float32 [rows, width] input and an output of the same width expected")
+        if rows is not None and (rows.dtype != torch.int32 or rows.numel() != out.shape[0]):
+            raise KernelError("layernorm: rows must be int32, one per output row")
+        self._call("hb_layernorm", x.data_ptr(), _rows(x, "layernorm input"), self._f32_vec(weight, n, "norm weight"),
+                   self._f32_vec(bias, n, "norm bias"), float(eps), out.data_ptr(), _code(out), _rows(out, "layernorm output"),
+                   rows.data_ptr() if rows is not None else None, out.shape[0], n, self._stream())
+        self.launches += 1
+
+    def layernorm_add(self, y, weight, bias, eps: float, x, copy=None, y2=None, sa: float = 1.0, sb: float = 1.0) -> None:
+        """``x += layernorm(y)`` row by row in 32-bit; with ``y2``: ``x += layernorm(sa * y + sb * y2)``; ``copy`` (same shape,
+        any kernel dtype) also receives the new rows of ``x``."""
+        self._dev(y, weight, bias, x, copy, y2)
+        T, n = x.shape
+        if x.dtype != torch.float32 or any(t is not None and (t.dtype != torch.float32 or tuple(t.shape) != (T, n)) for t in (y, y2)) \
+                or (copy is not None and tuple(copy.shape) != (T, n)):
+            raise KernelError("layernorm_add: float32 [tokens, width] inputs and residual expected")
+        self._call("hb_layernorm_add", y.data_ptr(), _rows(y, "layernorm_add input"), y2.data_ptr() if y2 is not None else None,
+                   _rows(y2, "layernorm_add input") if y2 is not None else 0, float(sa), float(sb), self._f32_vec(weight, n, "norm weight"),
+                   self._f32_vec(bias, n, "norm bias"), float(eps), x.data_ptr(), _rows(x, "residual"),
+                   copy.data_ptr() if copy is not None else None, _code(copy) if copy is not None else 0,
+                   _rows(copy, "residual copy") if copy is not None else 0, T, n, self._stream())
+        self.launches += 1
+
+    def convert(self, x, out) -> None:
+        """``out = x`` in ``out``'s dtype (``x`` float32, both contiguous)."""
+        self._dev(x, out)
+        if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or x.shape != out.shape:
+            raise KernelError("convert: contiguous float32 input and an output of the same shape expected")
+        self._call("hb_convert", x.data_ptr(), out.data_ptr(), _code(out), x.numel(), self._stream())
+        self.launches += 1
+
+    # ------------------------------------------------------------------ attention over one cached latent per token
+    def latent_prepare(self, proj, heads: int, d: int, dr: int, rank: int, down_at: int, c_weight, eps: float, table, rot: int,
+                       q_out, cache, step, append: bool) -> None:
+        """From a step's float32 projections ``[q (heads x (d + dr)) | ... ]`` with the down projection ``[latent (rank) | shared
+        key part (dr)]`` at column ``down_at``: the latent divided by its root mean square times ``c_weight`` and the key part
+        turned by ``table`` (pairs ``(2i, 2i + 1)`` of its first ``rot`` dimensions) into the cache (key row ``[c | k_r]``, value
+        row ``c``); every head's rotated query part turned into ``q_out[t, h, rank:]`` (``q_out`` ``[tokens, heads * (rank + dr)]``)."""
+        self._dev(proj, c_weight, table, q_out, cache.k, cache.v)
+        T = proj.shape[0]
+        if proj.dtype != torch.float32 or tuple(q_out.shape) != (T, heads * (rank + dr)):
+            raise KernelError("latent_prepare: float32 projections and queries [tokens, heads * (rank + dr)] expected")
+        if rot and (table is None or table.dtype != torch.float32 or not table.is_contiguous() or tuple(table.shape[:2]) != (T, rot // 2)):
+            raise KernelError("latent_prepare: rotary table does not match the tokens")
+        if tuple(cache.k.shape[1:]) != (1, 64, rank + dr) or tuple(cache.v.shape[1:]) != (1, 64, rank) \
+                or not cache.k.is_contiguous() or not cache.v.is_contiguous() or cache.k.dtype != cache.v.dtype:
+            raise KernelError("latent_prepare: cache layer does not match the latent")
+        pt = step.page_tables[cache.group]
+        self._call("hb_latent_prepare", proj.data_ptr(), _rows(proj, "projections"), heads, d, dr, rank, int(down_at),
+                   self._f32_vec(c_weight, rank, "latent norm weight"), float(eps), table.data_ptr() if rot else None, int(rot),
+                   q_out.data_ptr(), _code(q_out), _rows(q_out, "queries"), cache.k.data_ptr(), cache.v.data_ptr(), _code(cache.k),
+                   pt.data_ptr(), pt.shape[1], step.tok_seq.data_ptr(), step.positions.data_ptr(), T, cache.k.shape[0],
+                   1 if append else 0, self.status.data_ptr(), self._stream())
+        self.launches += 1
+
+    def head_linear(self, x, in_head: int, w, out, out_head: int, n_in: int, n_out: int, gate=None) -> None:
+        """``out[t, h * out_head : + n_out] = W_h x[t, h * in_head : + n_in]`` for every head h, ``w`` ``[heads, n_in, n_out]``
+        (``w[h, i, o] = W_h[o, i]``), ``x`` float32; with ``gate`` float32 ``[tokens, heads]`` times ``sigmoid(gate[t, h])``."""
+        self._dev(x, w, out, gate)
+        T, heads = x.shape[0], w.shape[0]
+        if x.dtype != torch.float32 or w.dim() != 3 or tuple(w.shape[1:]) != (n_in, n_out) or not w.is_contiguous() or out.shape[0] != T:
+            raise KernelError("head_linear: float32 input and weights [heads, n_in, n_out] expected")
+        if x.shape[1] < (heads - 1) * in_head + n_in or out.shape[1] < (heads - 1) * out_head + n_out:
+            raise KernelError("head_linear: rows are too short for the heads")
+        gp, ldg = self._head_gate(gate, T, heads)
+        self._call("hb_head_linear", x.data_ptr(), _rows(x, "head_linear input"), int(in_head), w.data_ptr(), _code(w), out.data_ptr(),
+                   _code(out), _rows(out, "head_linear output"), int(out_head), gp, ldg, T, heads, n_in, n_out, self._stream())
         self.launches += 1
 
     # ------------------------------------------------------------------ selective state-space scan

@@ -231,3 +231,65 @@ class SandwichBlock(Block):
             self.ff_norm.forward(x, h)
         self._run(self.ff, y, (h, y, step))
         return NORMED if self.ff_post.add_normed(y, x, then=ahead) else None
+
+
+class StreamCopyAhead(tuple):
+    """What a block whose sublayers read the residual stream itself asks of the block in front: ``(out,)``, the buffer
+    that should hold the stream's rows in the products' dtype when the block in front is done."""
+
+
+COPIED = "copied"       # what a block returns when it has left that copy
+
+
+@BLOCKS.register("postnorm")
+class PostNormBlock(Block):
+    """Norms on the sublayers' OUTPUTS only: ``x += post_a(mixer(x))``, then, if the layer has a feed-forward,
+    ``x += post_b(feed_forward(x))``.  The sublayers read the 32-bit stream ``x`` itself: in 32-bit mode directly, in
+    bfloat16 mode through a rounded copy, which the norm in front leaves while it adds to the stream (``add_normed(...,
+    copy=)``; only a stack's first block converts with a kernel of its own).  A sublayer writes its result to a 32-bit
+    buffer (parts with ``can_overwrite`` write it, for others it is zeroed and they add).  A mixer that is a weighted sum
+    of two branches (``forward_branches``) hands its two results to the norm, which sums them on the fly
+    (``add_normed_sum``)."""
+
+    ROLES = {"mixer": MIXERS, "mixer_post_norm": NORMS, "feed_forward": FEED_FORWARDS, "feed_forward_post_norm": NORMS}
+    OPTIONAL = ("feed_forward", "feed_forward_post_norm")
+    folds_norms = True
+
+    def __init__(self, layer_spec, ctx):
+        super().__init__(layer_spec, ctx)
+        p = self.parts
+        self.mixer, self.mixer_post = p["mixer"], p["mixer_post_norm"]
+        self.ff, self.ff_post = p.get("feed_forward"), p.get("feed_forward_post_norm")
+        if (self.ff is None) != (self.ff_post is None):
+            raise ValueError(f"layer {layer_spec.prefix!r}: a feed-forward and the norm on its output come together")
+        self.fuse_sum = True                # tests switch it off to run the weighted sum as a kernel of its own
+
+    def _copy_buffer(self, step, size: int):
+        return self.ctx.workspace.buffer("block.h", (self.ctx.max_step_tokens, size), self.ctx.dtype)[:step.num_tokens]
+
+    def fold_request(self, step):
+        size = getattr(self.mixer_post, "size", None)
+        if self.ctx.dtype == torch.float32 or size is None:
+            return None
+        return StreamCopyAhead((self._copy_buffer(step, size),))
+
+    def forward(self, x, step, cache, state, append: bool, prepared=None, prepare_next=None):
+        ws, cap, T = self.ctx.workspace, self.ctx.max_step_tokens, step.num_tokens
+        exact = self.ctx.dtype == torch.float32
+        h = x if exact else self._copy_buffer(step, x.shape[1])
+        if not exact and prepared is not COPIED:
+            self.ctx.ops.convert(x, h)
+        y = ws.buffer("block.branch", (cap, x.shape[1]), torch.float32)[:T]
+        ahead = prepare_next[0] if isinstance(prepare_next, StreamCopyAhead) else None
+        mixer_copy = None if exact else (h if self.ff is not None else ahead)
+        if self.fuse_sum and hasattr(self.mixer, "forward_branches") and hasattr(self.mixer_post, "add_normed_sum"):
+            (a, sa), (b, sb) = self.mixer.forward_branches(h, step, cache, state, append)
+            self.mixer_post.add_normed_sum(a, sa, b, sb, x, copy=mixer_copy)
+        else:
+            SandwichBlock._run(self.mixer, y, (h, y, step, cache, state, append))
+            self.mixer_post.add_normed(y, x, copy=mixer_copy)
+        if self.ff is None:
+            return COPIED if mixer_copy is not None else None
+        SandwichBlock._run(self.ff, y, (h, y, step))
+        self.ff_post.add_normed(y, x, copy=ahead)
+        return COPIED if ahead is not None else None

@@ -46,15 +46,16 @@ class LMHead(Part):
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
         self.tied = bool(spec.get("tied", False))
+        self.tensor_name = spec.get("tensor_name", "weight")      # behind the head's prefix
         self.weight = None
 
     def params(self) -> List[ParamSpec]:
         # a tied checkpoint may still carry a copy of the head; it is then not read
-        return [ParamSpec("weight", (self.vocab, self.hidden), absolute=True, optional=self.tied)]
+        return [ParamSpec(self.tensor_name, (self.vocab, self.hidden), absolute=True, optional=self.tied)]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         if not self.tied:
-            self.weight = self.ctx.ops.pack_weight(tensors["weight"].contiguous())
+            self.weight = self.ctx.ops.pack_weight(tensors[self.tensor_name].contiguous())
 
     def tie(self, embedding_weight: torch.Tensor):
         """The head reads the embedding table; returns the form it keeps it in (tiles, where the

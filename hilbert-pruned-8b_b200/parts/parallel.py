@@ -63,8 +63,23 @@ class ParallelMixers(Mixer):
         total = sum(self._state_sizes)
         return StateNeed((total,), torch.float32) if total else None
 
+    def forward_branches(self, h, step, cache, state, append: bool):
+        """Runs the branches and returns ``[(result, scale), (result, scale)]`` (32-bit buffers of the residual stream's
+        shape) for a caller that forms the weighted sum itself, in a kernel that reads it anyway."""
+        return list(zip(self._run_branches(h, step, cache, state, append), self.scales))
+
     def forward(self, h, residual, step, cache, state, append: bool, accumulate: bool = True):
-        ops, ws, T, cap = self.ctx.ops, self.ctx.workspace, step.num_tokens, self.ctx.max_step_tokens
+        ops = self.ctx.ops
+        outs = self._run_branches(h, step, cache, state, append)
+        if accumulate:
+            # residual += s0 a + s1 b: the sum first, in the first branch's buffer, then added
+            ops.scaled_sum(outs[0], self.scales[0], outs[1], self.scales[1], outs[0])
+            ops.scaled_sum(residual, 1.0, outs[0], 1.0, residual)
+        else:
+            ops.scaled_sum(outs[0], self.scales[0], outs[1], self.scales[1], residual)
+
+    def _run_branches(self, h, step, cache, state, append: bool):
+        ws, T, cap = self.ctx.workspace, step.num_tokens, self.ctx.max_step_tokens
         views = [] if cache is None else (list(cache) if isinstance(cache, (tuple, list)) else [cache])
         outs, at_c, at_s = [], 0, 0
         for i, m in enumerate(self.mixers):
@@ -81,9 +96,4 @@ class ParallelMixers(Mixer):
                 out.zero_()
                 m.forward(h, out, step, mine, st, append)
             outs.append(out)
-        if accumulate:
-            # residual += s0 a + s1 b: the sum first, in the first branch's buffer, then added
-            ops.scaled_sum(outs[0], self.scales[0], outs[1], self.scales[1], outs[0])
-            ops.scaled_sum(residual, 1.0, outs[0], 1.0, residual)
-        else:
-            ops.scaled_sum(outs[0], self.scales[0], outs[1], self.scales[1], residual)
+        return outs

@@ -1,7 +1,11 @@
 """Grouped-query attention with a sliding window that keeps the sequence's first tokens, and
 the options that go with it here: biases on the projections, queries and keys divided by their
-root mean square after the rotation, key and value heads of different sizes, softmax weights
-mixed between the heads, and values mixed with those of an earlier layer.
+root mean square after the rotation (or, ``qk_norm_weight``, divided by it and multiplied by a weight
+of the head's size, shared by the heads, BEFORE the rotation), key and value heads of different sizes,
+softmax weights mixed between the heads, values mixed with those of an earlier layer, and
+(``head_gate``) each head's result multiplied by ``sigmoid(Wg h)_head``, one number per token and head,
+before the output projection.  ``out_bias`` (default: as ``bias``) says whether the output projection has
+a bias too.
 
 Per token: ``q, k, v = Wq h + bq, Wk h + bk, Wv h + bv``; the position encoding turns q and k;
 ``q`` and ``k`` of every head are divided by ``sqrt(mean(x^2) + eps)`` (``qk_unit_norm``); with
@@ -40,6 +44,11 @@ class SinkAttention(Mixer):
         self.scale = float(p["scale"]) if p.get("scale") is not None else float(self.head_dim) ** -0.5
         self.bias = bool(p.get("bias", False))
         self.qk_unit_norm = bool(p.get("qk_unit_norm", False))
+        self.qk_norm_weight = bool(p.get("qk_norm_weight", False))
+        if self.qk_unit_norm and self.qk_norm_weight:
+            raise ValueError("attention: queries and keys get one norm, behind the rotation or in front of it")
+        self.head_gate = bool(p.get("head_gate", False))
+        self.out_bias = bool(p.get("out_bias", p.get("bias", False)))
         self.eps = float(p.get("eps", 1e-6))
         self.talk = bool(p.get("talk", False))
         self.v_mix = p.get("v_mix")                      # None | "first" | "mix"
@@ -52,10 +61,11 @@ class SinkAttention(Mixer):
         self.position = ctx.shared_part(POSITION_ENCODINGS, pos) if pos is not None else None
         self.graph_safe = getattr(self.position, "graph_safe", True)
         self.q_width, self.k_width, self.v_width = self.heads * self.head_dim, self.kv_heads * self.head_dim, self.kv_heads * self.v_dim
-        self.proj_width = self.q_width + self.k_width + self.v_width
+        self.gate_at = self.q_width + self.k_width + self.v_width
+        self.proj_width = self.gate_at + (self.heads if self.head_gate else 0)
         self.proj_ld = (self.proj_width + 7) // 8 * 8
         self.out_width = self.heads * self.v_dim
-        self.w_qkv = self.w_o = self.b_qkv = self.talk_matrix = self.v_lambda = None
+        self.w_qkv = self.w_o = self.b_qkv = self.talk_matrix = self.v_lambda = self.norm_weights = None
         self.use_heads_kernel = True          # tests switch it off to run the general kernel instead
 
     def params(self) -> List[ParamSpec]:
@@ -64,7 +74,13 @@ class SinkAttention(Mixer):
                ParamSpec("o", (W, self.out_width))]
         if self.bias:
             out += [ParamSpec("q.b", (self.q_width,), kind="vector", init="zeros"), ParamSpec("k.b", (self.k_width,), kind="vector", init="zeros"),
-                    ParamSpec("v.b", (self.v_width,), kind="vector", init="zeros"), ParamSpec("o.b", (W,), kind="vector", init="zeros")]
+                    ParamSpec("v.b", (self.v_width,), kind="vector", init="zeros")]
+        if self.out_bias:
+            out.append(ParamSpec("o.b", (W,), kind="vector", init="zeros"))
+        if self.qk_norm_weight:
+            out += [ParamSpec("q.norm", (self.head_dim,), kind="vector", init="ones"), ParamSpec("k.norm", (self.head_dim,), kind="vector", init="ones")]
+        if self.head_gate:
+            out.append(ParamSpec("g", (self.heads, W)))
         if self.talk:
             out.append(ParamSpec("talk", (self.heads, self.heads)))
         if self.v_mix is not None:
@@ -77,13 +93,18 @@ class SinkAttention(Mixer):
         q, k, v, o = t["q"], t["k"], t["v"], t["o"]
         if not (q.dtype == k.dtype == v.dtype):
             raise ValueError("attention: q, k and v projections are stored in different dtypes")
-        rows = [q, k, v]
+        rows = [q, k, v] + ([t["g"]] if self.head_gate else [])
+        if len({r.dtype for r in rows}) != 1:
+            raise ValueError("attention: the input projections are stored in different dtypes")
         if self.proj_ld > self.proj_width:
             rows.append(torch.zeros(self.proj_ld - self.proj_width, self.hidden, dtype=q.dtype, device=q.device))
         pack = self.ctx.ops.pack_weight
         self.w_qkv = pack(torch.cat(rows, dim=0).contiguous())
         if self.bias:
             self.b_qkv = torch.cat([t["q.b"].reshape(-1), t["k.b"].reshape(-1), t["v.b"].reshape(-1)]).to(torch.float32).contiguous()
+        if self.qk_norm_weight:
+            self.norm_weights = tuple(t[n].reshape(-1).to(torch.float32).contiguous() for n in ("q.norm", "k.norm"))
+        if self.out_bias:
             extra = torch.zeros(self.hidden, _BIAS_PAD, dtype=o.dtype, device=o.device)
             extra[:, 0] = t["o.b"].reshape(-1).to(o.dtype)
             o = torch.cat([o, extra], dim=1)
@@ -125,40 +146,52 @@ class SinkAttention(Mixer):
                 v_mode = 2
         q = ws.buffer("sink_attention.q", (cap, self.q_width), self.ctx.dtype)[:T]
         ops.qkv_prepare(proj, self.b_qkv, table, rot, H, G, d, dv, self.qk_unit_norm, self.eps, q, cache, step, append,
-                        self.v_lambda, v_first, v_mode)
-        ones = _BIAS_PAD if self.bias else 0
+                        self.v_lambda, v_first, v_mode, norm_weights=self.norm_weights)
+        ones = _BIAS_PAD if self.out_bias else 0
+        gate = proj[:, self.gate_at: self.gate_at + H] if self.head_gate else None
         attn = ws.buffer("sink_attention.out", (cap, self.out_width + ones), self.ctx.dtype)[:T]
-        longest = step.max_len if self.window is None else min(step.max_len, self.window + self.keep_first)
-        plan = ops.attention_heads_plan(T, H, G, d, dv, self.ctx.dtype, longest) if self.use_heads_kernel else None
-        if self.use_heads_kernel and ops.attention_sink_prefill_wanted(step, H, G, d, dv, self.ctx.dtype):
-            # many tokens: 64 query tokens of a sequence share a block's keys and values (flash-style, tensor cores)
-            all_values = self.talk and G > 1
-            n_val = G if all_values else 1
-            partial = ws.buffer("sink_attention.partial_general", (cap, H * n_val * dv), torch.float32)[:T]
-            ops.attention_sink_prefill(q, H, G, d, dv, cache, step, partial, self.scale, self.window, self.keep_first, all_values)
-            if n_val == G:
-                ops.head_mix_splits(partial, None, self.talk_matrix, attn, H, G, dv, 1, ones)
-            else:
-                ops.head_mix(partial, None, attn, H, G, dv, n_val, ones)
-        elif plan is not None:
-            # one block per (token, key split) serves all heads; it mixes the heads itself when it can
-            splits, writes_output = plan
-            if writes_output:
-                ops.attention_heads(q, H, G, d, dv, cache, step, self.scale, self.window, self.keep_first, 1,
-                                    mix=self.talk_matrix, out=attn, ones=ones)
-            else:
-                # tokens x splits at most: the same buffer for every step, a captured graph holds its address
-                rows = (ops.ATTENTION_HEADS_MAX_ROWS if ops.attention_heads_whole(H, G, d, dv, self.ctx.dtype)
-                        else max(cap, ops.ATTENTION_HEADS_MAX_ROWS))
-                partial = ws.buffer("sink_attention.partial", (rows, H * G * dv), torch.float32)
-                ml = ws.buffer("sink_attention.ml", (rows, H * 2), torch.float32)
-                ops.attention_heads(q, H, G, d, dv, cache, step, self.scale, self.window, self.keep_first, splits,
-                                    partial=partial, ml=ml)
-                ops.head_mix_splits(partial, ml, self.talk_matrix, attn, H, G, dv, splits, ones)
-        else:
-            all_values = self.talk and G > 1
-            n_val = G if all_values else 1
-            partial = ws.buffer("sink_attention.partial_general", (cap, H * n_val * dv), torch.float32)[:T]
-            ops.attention_sink(q, H, G, d, dv, cache, step, partial, self.scale, self.window, self.keep_first, all_values)
-            ops.head_mix(partial, self.talk_matrix, attn, H, G, dv, n_val, ones)
+        softmax_attention(self.ctx, q, H, G, d, dv, cache, step, self.scale, self.window, self.keep_first, attn, ones=ones, gate=gate,
+                          talk_matrix=self.talk_matrix if self.talk else None, use_heads_kernel=self.use_heads_kernel)
         ops.linear(attn, self.w_o, residual, accumulate=accumulate)
+
+
+def softmax_attention(ctx, q, H: int, G: int, d: int, dv: int, cache, step, scale: float, window: Optional[int], keep_first: int, out,
+                      ones: int = 0, gate=None, talk_matrix=None, use_heads_kernel: bool = True) -> None:
+    """Softmax attention of the step's queries ``q [tokens, H * d]`` over the cached keys and values of ``cache`` (``G``
+    key/value heads of sizes ``d`` and ``dv``), by whichever kernel takes the step: ``out [tokens, H * dv + ones]`` (the
+    dtype of the products, or 32-bit) receives the normalised results, mixed between the heads by ``talk_matrix``, each
+    head's times ``sigmoid(gate[t, head])``, and ``ones`` more columns (a one, then zeros).  Any part that has put its keys
+    and values into a paged cache group can call it."""
+    ops, ws, T, cap = ctx.ops, ctx.workspace, step.num_tokens, ctx.max_step_tokens
+    talk = talk_matrix is not None
+    longest = step.max_len if window is None else min(step.max_len, window + keep_first)
+    plan = ops.attention_heads_plan(T, H, G, d, dv, ctx.dtype, longest) if use_heads_kernel else None
+    if use_heads_kernel and ops.attention_sink_prefill_wanted(step, H, G, d, dv, ctx.dtype):
+        # many tokens: 64 query tokens of a sequence share a block's keys and values (flash-style, tensor cores)
+        all_values = talk and G > 1
+        n_val = G if all_values else 1
+        partial = ws.buffer("sink_attention.partial_general", (cap, H * n_val * dv), torch.float32)[:T]
+        ops.attention_sink_prefill(q, H, G, d, dv, cache, step, partial, scale, window, keep_first, all_values)
+        if n_val == G:
+            ops.head_mix_splits(partial, None, talk_matrix, out, H, G, dv, 1, ones, gate=gate)
+        else:
+            ops.head_mix(partial, None, out, H, G, dv, n_val, ones, gate=gate)
+    elif plan is not None:
+        # one block per (token, key split) serves all heads; it mixes the heads itself when it can
+        splits, writes_output = plan
+        if writes_output and gate is None and out.dtype == ctx.dtype:
+            ops.attention_heads(q, H, G, d, dv, cache, step, scale, window, keep_first, 1, mix=talk_matrix, out=out, ones=ones)
+        else:
+            # tokens x splits at most: the same buffer for every step, a captured graph holds its address
+            rows = (ops.ATTENTION_HEADS_MAX_ROWS if ops.attention_heads_whole(H, G, d, dv, ctx.dtype)
+                    else max(cap, ops.ATTENTION_HEADS_MAX_ROWS))
+            partial = ws.buffer("sink_attention.partial", (rows, H * G * dv), torch.float32)
+            ml = ws.buffer("sink_attention.ml", (rows, H * 2), torch.float32)
+            ops.attention_heads(q, H, G, d, dv, cache, step, scale, window, keep_first, splits, partial=partial, ml=ml)
+            ops.head_mix_splits(partial, ml, talk_matrix, out, H, G, dv, splits, ones, gate=gate)
+    else:
+        all_values = talk and G > 1
+        n_val = G if all_values else 1
+        partial = ws.buffer("sink_attention.partial_general", (cap, H * n_val * dv), torch.float32)[:T]
+        ops.attention_sink(q, H, G, d, dv, cache, step, partial, scale, window, keep_first, all_values)
+        ops.head_mix(partial, talk_matrix, out, H, G, dv, n_val, ones, gate=gate)
