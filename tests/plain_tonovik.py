@@ -189,6 +189,18 @@ class PlainTonovik:
         logits = r(layer_norm(x, w["final.norm"], w["final.norm.b"], eps)) @ w["head"].T
         return (logits, torch.stack(layers)) if return_layers else logits
 
+    def logits(self, tokens: List[int]):
+        return self.forward(tokens).to(torch.float64)
+
+
+def latent_heads(q, c, k_rot, uk, uv, scale: float):
+    """The latent attention with every head's keys and values written out: q [T, H, d + dr] (rotated part last, already
+    turned), c [T, rank], k_rot [T, dr] (turned), uk [H * d, rank], uv [H * dv, rank] -> [T, H, dv]."""
+    T, H, _ = q.shape
+    d, dv = uk.shape[0] // H, uv.shape[0] // H
+    k = torch.cat([(c @ uk.T).reshape(T, H, d), k_rot[:, None, :].expand(T, H, k_rot.shape[1])], dim=-1)
+    return masked_softmax_attention(q, k, (c @ uv.T).reshape(T, H, dv), scale, None)
+
 
 def generate_greedy(model: PlainTonovik, prompt, n: int) -> List[int]:
     seq = list(prompt)
