@@ -5,6 +5,7 @@
     python bench.py --timeline --layers 3 --skip-points    # per-kernel times inside the decode graph
     python bench.py --design pogezen      # a line of its own: the Pogezen design beside Llama layers of equal size
     python bench.py --design vuladra      # a line of its own: the Vuladra design beside Pogezen layers of equal size
+    python bench.py --design tonovik      # a line of its own: the Tonovik design beside Vuladra layers of equal size
 
 Prints ONE JSON line.  A step is one decode step of a batch of 8 sequences whose caches hold
 about 8192 tokens each; ``value`` is decoded tokens per second from CUDA events around the
@@ -447,6 +448,26 @@ def vuladra_config(z):
             "layers": [dict(scan, mlp=dense), dict(att, mlp=moe), dict(par, mlp=moe), dict(scan, mlp=moe)]}
 
 
+# --design tonovik: four Tonovik layers (attention over cached latents; softmax window attention beside a decayed matrix
+# memory, twice; attention over cached latents; a dense feed-forward behind each) beside the four Vuladra layers above, the
+# library's closest model (it has the same pair of window attention and decayed memory side by side), at the same width,
+# heads, head size and window.  The latent has four times the head size (512 at head size 128), the rotated part half of it.
+def tonovik_config(z):
+    W, hd = z["width"], z["head_dim"]
+    lat = {"type": "latent_attention", "mixer": {
+        "heads": z["heads"], "dim": hd, "rot_dim": hd // 2, "vdim": hd, "kv_rank": 4 * hd, "scale": (1.5 * hd) ** -0.5,
+        "rot": {"base": 10000.0, "dims": hd // 2, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": DESIGN_WINDOW},
+                 "rot": {"base": 500000.0, "dims": hd}},
+        "right": {"heads": z["ml_heads"], "dim": z["ml_dim"], "vdim": W // z["ml_heads"],
+                  "decay": [1.0 - 2.0 ** -(3 + i) for i in range(z["ml_heads"])], "rot": {"base": 10000.0, "dims": z["ml_dim"]}},
+        "left_scale": 1.0, "right_scale": 1.0}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    return {"architecture": "Tonovik", "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "vocab": DESIGN_VOCAB, "width": W,
+            "layers": [dict(lat, mlp=dense), dict(par, mlp=dense), dict(par, mlp=dense), dict(lat, mlp=dense)]}
+
+
 def llama_like_config(z):
     return dict(MODEL_8B, hidden_size=z["width"], num_hidden_layers=4, intermediate_size=z["ff"], vocab_size=DESIGN_VOCAB,
                 num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["head_dim"], tie_word_embeddings=True)
@@ -495,7 +516,9 @@ def design_comparison(a) -> int:
     out = {}
     for size, z in DESIGN_SIZES.items():
         row = {}
-        if a.design == "vuladra":
+        if a.design == "tonovik":
+            pair = (("tonovik", hb.TonovikConfig.from_dict(tonovik_config(z))), ("vuladra", hb.VuladraConfig.from_dict(vuladra_config(z))))
+        elif a.design == "vuladra":
             pair = (("vuladra", hb.VuladraConfig.from_dict(vuladra_config(z))), ("pogezen", hb.PogezenConfig.from_dict(pogezen_config(z))))
         else:
             pair = (("pogezen", hb.PogezenConfig.from_dict(pogezen_config(z))), ("llama", hb.LlamaConfig.from_dict(llama_like_config(z))))
@@ -530,7 +553,8 @@ def design_comparison(a) -> int:
             del llm, eng, seqs
             torch.cuda.empty_cache()
         out[size] = row
-    names = "Vuladra layers beside Pogezen layers" if a.design == "vuladra" else "Pogezen layers beside Llama layers"
+    names = {"tonovik": "Tonovik layers beside Vuladra layers", "vuladra": "Vuladra layers beside Pogezen layers",
+             "pogezen": "Pogezen layers beside Llama layers"}[a.design]
     print(json.dumps({"metric": f"{names} of equal size: prefill of one 2048-token prompt and decode "
                                 f"steps of batch {batch} at context {context}, four layers, random weights",
                       "unit": "tokens/s", "dtype": "bf16", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
@@ -634,8 +658,8 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=("8b", "3b", "1b"), default="8b",
                     help="8b: the default line; 3b, 1b: the generation workloads at those shapes (--steps = repeats)")
-    ap.add_argument("--design", choices=("pogezen", "vuladra"), default=None,
-                    help="a line of its own: this design's layers beside Llama layers of equal size (prefill, decode, "
+    ap.add_argument("--design", choices=("pogezen", "vuladra", "tonovik"), default=None,
+                    help="a line of its own: this design's layers beside layers of equal size of the closest other design (prefill, decode, "
                          "device time per kernel); the default workload is not run")
     ap.add_argument("--timeline", action="store_true",
                     help="print the per-kernel times of a decode step inside the replayed graph (builds the "

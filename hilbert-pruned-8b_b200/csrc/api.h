@@ -202,9 +202,14 @@ int hb_layernorm_add(const float* y, long long ldy, const float* y2, long long l
 int hb_convert(const float* x, void* out, int out_dtype, long long n, void* stream);
 // Attention over one cached latent per token (latent_attention.cu): the cache rows, and the per-head products around it
 int hb_latent_prepare(const float* proj, long long ldp, int n_heads, int d, int dr, int rank, int down_at, const float* c_weight, float eps,
-                      const float* table, int rot, void* q_out, int q_dtype, long long ldq, void* k_cache, void* v_cache, int cache_dtype,
-                      const int* page_table, int pt_width, const int* tok_seq, const int* positions, int n_tokens, int n_pages, int append,
-                      int* status, void* stream);
+                      const float* table, int rot, void* q_out, int q_dtype, long long ldq, int q_head, int q_rot_at, int q_copy, void* k_cache,
+                      void* v_cache, int cache_dtype, const int* page_table, int pt_width, const int* tok_seq, const int* positions, int n_tokens,
+                      int n_pages, int append, int* status, void* stream);
+int hb_latent_gather(const void* v_cache, const int* page_table, int pt_width, const int* seq_len, int n_seqs, int max_pages, int rank,
+                     void* rows, int* scratch_table, int scratch_width, int n_pages, int* status, void* stream);
+int hb_latent_scatter(const void* kv, long long ldkv, const void* k_cache, const int* page_table, int pt_width, const int* seq_len, int n_seqs,
+                      int max_pages, int n_heads, int d, int dr, int dv, int rank, int hd_out, int vd_out, void* k_out, void* v_out, int n_pages,
+                      void* stream);
 int hb_head_linear(const float* in, long long ldi, long long in_head, const void* w, int w_dtype, void* out, int out_dtype, long long ldo,
                    long long out_head, const float* gate, long long ldg, int n_tokens, int n_heads, int n_in, int n_out, void* stream);
 // Short causal convolution with bias, activation and state; selective state-space scan (selective_scan.cu)

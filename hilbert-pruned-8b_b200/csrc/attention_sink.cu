@@ -438,7 +438,30 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
         copy_rows(k_cache, Ks, hd, kst, kcpr);
         copy_rows(v_cache, Vs, vd, vst, vcpr);
         __syncthreads();
-        // scores: thread (kv head, key), the heads of the group one after the other
+        // scores.  Few key/value heads (their keys of a tile would occupy less than half of the threads): thread
+        // (head, key), the key row read once per head; the sum runs over the dimensions in the same order either way
+        if (nkv * KT * 2 <= AH_THREADS) {
+            for (int i = tid; i < nh * KT; i += AH_THREADS) {
+                const int h = i / KT, r = i - h * KT;
+                const TC* kr = Ks + (size_t)r * kst + (h / group) * hd;
+                const float4* qh = reinterpret_cast<const float4*>(qs + h * hd);
+                float dot = 0.0f;
+                for (int d0 = 0; d0 < hd; d0 += CE) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(kr + d0);
+                    const TC* kv = reinterpret_cast<const TC*>(&raw);
+#pragma unroll
+                    for (int e = 0; e < CE; e += 4) {
+                        const float4 qv = qh[(d0 + e) >> 2];
+                        dot = fmaf(qv.x, to_f32(kv[e]), dot);
+                        dot = fmaf(qv.y, to_f32(kv[e + 1]), dot);
+                        dot = fmaf(qv.z, to_f32(kv[e + 2]), dot);
+                        dot = fmaf(qv.w, to_f32(kv[e + 3]), dot);
+                    }
+                }
+                Ss[h * KT + r] = (v0 + r < v_end && page_of[r] >= 0) ? dot * scale : -INFINITY;
+            }
+        } else
+        // many key/value heads: thread (kv head, key), the heads of the group one after the other
         for (int i = tid; i < nkv * KT; i += AH_THREADS) {
             const int g = i / KT, r = i - g * KT;
             const TC* kr = Ks + (size_t)r * kst + g * hd;

@@ -13,7 +13,7 @@
 // and lo = bf16(w - hi), added in the float32 accumulator: exact to 16 mantissa bits.  The result is
 // normalised and written in float32: out[token][head][value head (or 0)][v_dim].
 //
-// Sizes: key and value head sizes 64 or 128 each; any head and group counts.
+// Sizes: key heads of 64, 128, 192 or 256, value heads of 64 or 128; any head and group counts.
 #include "api.h"
 #include "mma.cuh"
 
@@ -230,7 +230,8 @@ attn_sink_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const b
 }
 
 extern "C" int hb_attention_sink_prefill_supported(int n_heads, int n_kv_heads, int head_dim, int v_dim) {
-    return (head_dim == 64 || head_dim == 128) && (v_dim == 64 || v_dim == 128) && n_kv_heads > 0 && n_heads % n_kv_heads == 0;
+    return (head_dim == 64 || head_dim == 128 || head_dim == 192 || head_dim == 256) && (v_dim == 64 || v_dim == 128) && n_kv_heads > 0
+           && n_heads % n_kv_heads == 0;
 }
 
 template <int HD, int VD>
@@ -259,7 +260,7 @@ extern "C" int hb_attention_sink_prefill(const void* q, long long q_stride, cons
                                          int n_val, float scale, int window, int keep_first, int n_pages, int* status, void* stream) {
     if (n_seqs == 0 || q_blocks == 0) return 0;
     HB_REQUIRE(hb_attention_sink_prefill_supported(n_heads, n_kv_heads, head_dim, v_dim),
-               "attention_sink_prefill: head sizes %d and %d are not built (64 or 128 each)", head_dim, v_dim);
+               "attention_sink_prefill: head sizes %d and %d are not built (keys 64 to 256 in steps of 64, values 64 or 128)", head_dim, v_dim);
     HB_REQUIRE(n_seqs > 0 && q_blocks > 0 && q_blocks <= 65535 && window >= 0 && keep_first >= 0, "attention_sink_prefill: bad sizes");
     HB_REQUIRE(n_val == 1 || (n_val == n_kv_heads && n_val <= 65535), "attention_sink_prefill: %d value heads per head, 1 or %d expected", n_val, n_kv_heads);
     HB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q & 3) == 0 && ((uintptr_t)out & 7) == 0, "attention_sink_prefill: queries and output must be aligned");
@@ -268,6 +269,10 @@ extern "C" int hb_attention_sink_prefill(const void* q, long long q_stride, cons
 #define HB_SP(HD, VD)                                                                                                                     \
     return launch_sink_prefill<HD, VD>(q, q_stride, k_cache, v_cache, page_table, pt_width, seq_start, seq_pos0, out, n_seqs, q_blocks, n_heads, \
                                        n_kv_heads, n_val, scale, window, keep_first, n_pages, status, s)
+    if (head_dim == 256 && v_dim == 128) HB_SP(256, 128);
+    if (head_dim == 256 && v_dim == 64) HB_SP(256, 64);
+    if (head_dim == 192 && v_dim == 128) HB_SP(192, 128);
+    if (head_dim == 192 && v_dim == 64) HB_SP(192, 64);
     if (head_dim == 128 && v_dim == 128) HB_SP(128, 128);
     if (head_dim == 128 && v_dim == 64) HB_SP(128, 64);
     if (head_dim == 64 && v_dim == 128) HB_SP(64, 128);

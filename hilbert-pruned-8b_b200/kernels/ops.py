@@ -96,7 +96,10 @@ _SIGNATURES = {
                          _c_int, _c_int, _c_ptr],
     "hb_convert": [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr],
     "hb_latent_prepare": [_c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_int, _c_ll,
-                          _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+                          _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_latent_gather": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_latent_scatter": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                          _c_ptr, _c_ptr, _c_int, _c_ptr],
     "hb_head_linear": [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_int, _c_ptr, _c_int, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int,
                        _c_ptr],
     "hb_conv_act": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int,
@@ -1223,14 +1226,17 @@ class Ops:
 
     # ------------------------------------------------------------------ attention over one cached latent per token
     def latent_prepare(self, proj, heads: int, d: int, dr: int, rank: int, down_at: int, c_weight, eps: float, table, rot: int,
-                       q_out, cache, step, append: bool) -> None:
+                       q_out, cache, step, append: bool, whole_heads: int = 0) -> None:
         """From a step's float32 projections ``[q (heads x (d + dr)) | ... ]`` with the down projection ``[latent (rank) | shared
         key part (dr)]`` at column ``down_at``: the latent divided by its root mean square times ``c_weight`` and the key part
         turned by ``table`` (pairs ``(2i, 2i + 1)`` of its first ``rot`` dimensions) into the cache (key row ``[c | k_r]``, value
-        row ``c``); every head's rotated query part turned into ``q_out[t, h, rank:]`` (``q_out`` ``[tokens, heads * (rank + dr)]``)."""
+        row ``c``); every head's rotated query part turned into ``q_out[t, h, rank:]`` (``q_out`` ``[tokens, heads * (rank + dr)]``).
+        With ``whole_heads`` = n: ``q_out`` is ``[tokens, heads * n]`` and receives every head's whole query, ``[unrotated (d) |
+        rotated and turned (dr) | zeros]``."""
         self._dev(proj, c_weight, table, q_out, cache.k, cache.v)
         T = proj.shape[0]
-        if proj.dtype != torch.float32 or tuple(q_out.shape) != (T, heads * (rank + dr)):
+        q_head = int(whole_heads) if whole_heads else rank + dr
+        if proj.dtype != torch.float32 or tuple(q_out.shape) != (T, heads * q_head) or q_head < (d + dr if whole_heads else 0):
             raise KernelError("latent_prepare: float32 projections and queries [tokens, heads * (rank + dr)] expected")
         if rot and (table is None or table.dtype != torch.float32 or not table.is_contiguous() or tuple(table.shape[:2]) != (T, rot // 2)):
             raise KernelError("latent_prepare: rotary table does not match the tokens")
@@ -1240,9 +1246,44 @@ class Ops:
         pt = step.page_tables[cache.group]
         self._call("hb_latent_prepare", proj.data_ptr(), _rows(proj, "projections"), heads, d, dr, rank, int(down_at),
                    self._f32_vec(c_weight, rank, "latent norm weight"), float(eps), table.data_ptr() if rot else None, int(rot),
-                   q_out.data_ptr(), _code(q_out), _rows(q_out, "queries"), cache.k.data_ptr(), cache.v.data_ptr(), _code(cache.k),
+                   q_out.data_ptr(), _code(q_out), _rows(q_out, "queries"), q_head, d if whole_heads else rank, d if whole_heads else 0,
+                   cache.k.data_ptr(), cache.v.data_ptr(), _code(cache.k),
                    pt.data_ptr(), pt.shape[1], step.tok_seq.data_ptr(), step.positions.data_ptr(), T, cache.k.shape[0],
                    1 if append else 0, self.status.data_ptr(), self._stream())
+        self.launches += 1
+
+    def latent_gather(self, cache, step, rank: int, rows, scratch_table) -> None:
+        """The latents of the step's sequences, from their first token on, page by page: ``rows`` bfloat16 ``[pages * 64, rank]``
+        (sequence b's pages follow those of the sequences in front of it; rows behind a sequence's end are zeros) and the page
+        table of that layout, ``scratch_table`` int32 ``[sequences, width]``."""
+        self._dev(cache.v, rows, scratch_table)
+        pages = sum((n + 63) // 64 for n in step.host_len)
+        if cache.v.dtype != torch.bfloat16 or rows.dtype != torch.bfloat16 or not rows.is_contiguous() or tuple(rows.shape) != (pages * 64, rank) \
+                or tuple(cache.v.shape[1:]) != (1, 64, rank) or not cache.v.is_contiguous():
+            raise KernelError("latent_gather: bfloat16 cache [pages, 1, 64, rank] and rows [step pages * 64, rank] expected")
+        if scratch_table.dtype != torch.int32 or not scratch_table.is_contiguous() or scratch_table.shape[0] != step.num_seqs \
+                or scratch_table.shape[1] < (step.max_len + 63) // 64:
+            raise KernelError("latent_gather: the scratch page table must be int32 [sequences, pages of the longest]")
+        pt = step.page_tables[cache.group]
+        self._call("hb_latent_gather", cache.v.data_ptr(), pt.data_ptr(), pt.shape[1], step.seq_len.data_ptr(), step.num_seqs,
+                   (step.max_len + 63) // 64, rank, rows.data_ptr(), scratch_table.data_ptr(), scratch_table.shape[1], cache.v.shape[0],
+                   self.status.data_ptr(), self._stream())
+        self.launches += 1
+
+    def latent_scatter(self, kv, cache, step, heads: int, d: int, dr: int, dv: int, rank: int, k_out, v_out) -> None:
+        """From ``kv`` bfloat16 ``[pages * 64, >= heads * (d + dv)]`` = ``[k_u (heads x d) | v (heads x dv)]`` per gathered row and the
+        cached rotated key parts: ``k_out`` ``[pages, heads, 64, >= d + dr]`` = ``[k_u | k_r | zeros]`` and ``v_out`` ``[pages, heads, 64,
+        >= dv]`` = ``[v | zeros]``, the paged layout of a cache with as many key/value heads as heads."""
+        self._dev(kv, cache.k, k_out, v_out)
+        pages = sum((n + 63) // 64 for n in step.host_len)
+        if any(t.dtype != torch.bfloat16 for t in (kv, cache.k, k_out, v_out)) or kv.shape[0] != pages * 64 or kv.stride(1) != 1 \
+                or not k_out.is_contiguous() or not v_out.is_contiguous() or tuple(k_out.shape[:3]) != (pages, heads, 64) \
+                or tuple(v_out.shape[:3]) != (pages, heads, 64) or tuple(cache.k.shape[1:]) != (1, 64, rank + dr):
+            raise KernelError("latent_scatter: bfloat16 rows [step pages * 64, ..] and outputs [step pages, heads, 64, ..] expected")
+        pt = step.page_tables[cache.group]
+        self._call("hb_latent_scatter", kv.data_ptr(), _rows(kv, "keys and values"), cache.k.data_ptr(), pt.data_ptr(), pt.shape[1],
+                   step.seq_len.data_ptr(), step.num_seqs, (step.max_len + 63) // 64, heads, d, dr, dv, rank, k_out.shape[3], v_out.shape[3],
+                   k_out.data_ptr(), v_out.data_ptr(), cache.k.shape[0], self._stream())
         self.launches += 1
 
     def head_linear(self, x, in_head: int, w, out, out_head: int, n_in: int, n_out: int, gate=None) -> None:

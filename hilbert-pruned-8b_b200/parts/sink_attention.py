@@ -170,7 +170,7 @@ def softmax_attention(ctx, q, H: int, G: int, d: int, dv: int, cache, step, scal
         # many tokens: 64 query tokens of a sequence share a block's keys and values (flash-style, tensor cores)
         all_values = talk and G > 1
         n_val = G if all_values else 1
-        partial = ws.buffer("sink_attention.partial_general", (cap, H * n_val * dv), torch.float32)[:T]
+        partial = ws.buffer(f"sink_attention.partial_general.{H * n_val * dv}", (cap, H * n_val * dv), torch.float32)[:T]
         ops.attention_sink_prefill(q, H, G, d, dv, cache, step, partial, scale, window, keep_first, all_values)
         if n_val == G:
             ops.head_mix_splits(partial, None, talk_matrix, out, H, G, dv, 1, ones, gate=gate)
@@ -179,11 +179,13 @@ def softmax_attention(ctx, q, H: int, G: int, d: int, dv: int, cache, step, scal
     elif plan is not None:
         # one block per (token, key split) serves all heads; it mixes the heads itself when it can
         splits, writes_output = plan
-        if writes_output and gate is None and out.dtype == ctx.dtype:
+        direct = gate is None and out.dtype == ctx.dtype          # the kernel can write this output itself
+        if writes_output and direct:
             ops.attention_heads(q, H, G, d, dv, cache, step, scale, window, keep_first, 1, mix=talk_matrix, out=out, ones=ones)
         else:
-            # tokens x splits at most: the same buffer for every step, a captured graph holds its address
-            rows = (ops.ATTENTION_HEADS_MAX_ROWS if ops.attention_heads_whole(H, G, d, dv, ctx.dtype)
+            # tokens x splits at most: the same buffer for every step, a captured graph holds its address.  Only steps of few
+            # tokens are split when the kernel writes the output of the others itself; else every token of a step has a row.
+            rows = (ops.ATTENTION_HEADS_MAX_ROWS if direct and ops.attention_heads_whole(H, G, d, dv, ctx.dtype)
                     else max(cap, ops.ATTENTION_HEADS_MAX_ROWS))
             partial = ws.buffer("sink_attention.partial", (rows, H * G * dv), torch.float32)
             ml = ws.buffer("sink_attention.ml", (rows, H * 2), torch.float32)
@@ -192,6 +194,6 @@ def softmax_attention(ctx, q, H: int, G: int, d: int, dv: int, cache, step, scal
     else:
         all_values = talk and G > 1
         n_val = G if all_values else 1
-        partial = ws.buffer("sink_attention.partial_general", (cap, H * n_val * dv), torch.float32)[:T]
+        partial = ws.buffer(f"sink_attention.partial_general.{H * n_val * dv}", (cap, H * n_val * dv), torch.float32)[:T]
         ops.attention_sink(q, H, G, d, dv, cache, step, partial, scale, window, keep_first, all_values)
         ops.head_mix(partial, talk_matrix, out, H, G, dv, n_val, ones, gate=gate)

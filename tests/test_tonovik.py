@@ -22,12 +22,14 @@ DEV = "cuda:0"
 # --------------------------------------------------------------------------- helpers
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
-    """name -> (folder, config, {dtype: plain model}); the bfloat16 one rounds where the library does"""
+    """name -> (folder, config, {"exact" | dtype: plain model}): in 64-bit; in 32-bit; in 64-bit but rounding to bfloat16
+    where the library does"""
     out = {}
     for i, (name, cfg) in enumerate(tv.CONFIGS.items()):
         d = str(tmp_path_factory.mktemp("tonovik_" + name))
         tensors = tv.write_model(d, cfg, 40 + i)
-        out[name] = (d, cfg, {"float32": PlainTonovik(cfg, tensors), "bfloat16": PlainTonovik(cfg, tensors, round_to=torch.bfloat16)})
+        out[name] = (d, cfg, {"exact": PlainTonovik(cfg, tensors), "float32": PlainTonovik(cfg, tensors, dtype=torch.float32),
+                              "bfloat16": PlainTonovik(cfg, tensors, round_to=torch.bfloat16)})
     return out
 
 
@@ -36,27 +38,66 @@ def _engine(folder, dtype, max_tokens, **kw):
     return Engine.from_folder(folder, dtype, max_tokens=max_tokens, **kw)
 
 
-def _reference(plain, requests):
+def _err(x, exact):
+    return (x - exact).abs().max().item() / max(1.0, exact.abs().max().item())
+
+
+def _spread(x, exact, scale):
+    """Root mean square over the vocabulary of the difference, its mean taken off, over ``scale``."""
+    d = (x - exact).double()
+    return (d - d.mean()).pow(2).mean().sqrt().item() / scale
+
+
+def _reference(plain, requests, dtype=None):
+    """(request, position) -> (the exact logits; the two errors, ``_err`` and ``_spread``, of a plain model that rounds as
+    ``dtype`` does).  ``_spread`` is in units of the root mean square of all the exact logits (each row's mean taken off)."""
+    exact = {rid: plain["exact"].logits(toks) for rid, toks in requests.items()}
+    rows = torch.cat([e.double() - e.double().mean(dim=-1, keepdim=True) for e in exact.values()])
+    scale = max(rows.pow(2).mean().sqrt().item(), 1e-30)
     ref = {}
     for rid, toks in requests.items():
-        lg = plain.logits(toks)
+        rounded = plain[dtype].logits(toks) if dtype is not None else exact[rid]
         for p in range(len(toks)):
-            ref[(rid, p)] = lg[p]
+            ref[(rid, p)] = (exact[rid][p], _err(rounded[p], exact[rid][p]), _spread(rounded[p], exact[rid][p], scale), scale)
     return ref
 
 
-# Fixed bounds.  float32: the largest difference of a position is at most 1e-4 of that position's largest logit (or of 1)
-# against the 64-bit plain model, at every position.  bfloat16: at most 4 % of it against the plain model that rounds what
-# the matrix products read and what the cache holds to bfloat16 (the library rounds a query after the key up-projection
-# is folded into it, the plain model before: the two differ by roundings, not by more).
+# The bound.  Every position's logits are compared with the 64-bit plain model's.  In this design a layer norm sits on each
+# sublayer's OUTPUT, so where that output happens to have little spread the norm multiplies whatever rounding error it
+# carries: a few positions of a random model are ill-conditioned, and there a plain model that only rounds (to 32-bit; or
+# what the matrix products read and the cache holds to bfloat16) is itself far from the exact one.
+# 32-bit: the largest difference over the largest logit (or 1) is at most three times what the plain 32-bit model shows at
+# that position, or three times that model's median, or 1e-4, at EVERY position.
+# bfloat16: which positions a rounding hits hard differs between two programs that round in different places, so the
+# library's errors are compared with the plain rounding model's as a population (root mean square over the vocabulary):
+# at most 3 % of the positions (or one) above three times the plain model's error there (or its median), the median and
+# the ninth decile within 1.5 times the plain model's, the largest within three times its largest.  A wrong key, window
+# or state moves the logits by tens of per cent at most positions of these models, and the 32-bit runs of the same
+# schedules hold every single position.
 def _compare(got, ref, dtype, what):
     assert got, "nothing was compared"
     for key, g in got.items():
-        r = ref[key]
         assert torch.isfinite(g).all(), f"{what}: non-finite logits at {key}"
-        err = (g - r).abs().max().item() / max(1.0, r.abs().max().item())
-        bound = 1e-4 if dtype == "float32" else 4e-2
-        assert err <= bound, f"{what}: {dtype} logits differ at request {key[0]} position {key[1]}: {err:.3e}"
+    if dtype == "float32":
+        noise = sorted(ref[key][1] for key in got)
+        typical = noise[len(noise) // 2]
+        for key, g in got.items():
+            exact, rounding = ref[key][:2]
+            bound = max(3.0 * max(rounding, typical), 1e-4)
+            err = _err(g, exact)
+            assert err <= bound, f"{what}: float32 logits differ at request {key[0]} position {key[1]}: {err:.3e} (bound {bound:.3e})"
+        return
+    keys = list(got)
+    noise = [ref[k][2] for k in keys]
+    errs = [_spread(got[k], ref[k][0], ref[k][3]) for k in keys]
+    n, ns, es = len(keys), sorted(noise), sorted(errs)
+    typical = ns[n // 2]
+    over = [(e / (3.0 * max(x, typical)), k) for k, e, x in zip(keys, errs, noise) if e > 3.0 * max(x, typical)]
+    assert len(over) <= max(1, (3 * n) // 100), f"{what}: bfloat16 logits differ at {len(over)} of {n} positions, most at {max(over)}"
+    assert es[-1] <= 3.0 * max(ns[-1], 3.0 * typical), f"{what}: largest bfloat16 error {es[-1]:.3e}, the plain rounding model's {ns[-1]:.3e}"
+    if n >= 40:
+        assert es[n // 2] <= 1.5 * typical, f"{what}: median bfloat16 error {es[n // 2]:.3e}, the plain rounding model's {typical:.3e}"
+        assert es[(9 * n) // 10] <= 1.5 * ns[(9 * n) // 10], f"{what}: ninth decile {es[(9 * n) // 10]:.3e} against {ns[(9 * n) // 10]:.3e}"
 
 
 def _requests(cfg, lengths, seed):
@@ -426,6 +467,41 @@ def test_latent_attention_finds_a_far_key(H, d, dr, dv, rank, scaling, dims, dty
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("H,d,dr,dv,rank", [(4, 32, 32, 64, 64), (3, 64, 32, 64, 128), (2, 100, 28, 40, 48), (2, 128, 64, 128, 96), (5, 160, 64, 72, 64),
+                                            (2, 8, 8, 200, 32)])
+def test_latent_attention_with_keys_and_values_written_out_equals_the_folded_form(H, d, dr, dv, rank):
+    """bfloat16 steps of many tokens write every head's keys and values out for the tensor-core prompt kernel (head sizes
+    padded to 64, 128, 192 or 256 for keys and 64 or 128 for values; larger ones stay folded): the same results as the folded
+    form, for prompts that start a sequence and for portions that go on in one, beside a second, shorter sequence."""
+    require_gpu()
+    layer = tv.latent(H, d, dr, dv, rank, scaling=(2.0, 64, 8.0, 1.0))
+    W = 96
+    spec = _mixer_spec(layer, W)
+    g = torch.Generator().manual_seed(rank + d)
+    wts = _random_weights(_params_of(spec), g, gain=2.0)
+    hs = [torch.randn(n, W, generator=g) for n in (333, 70)]
+    c = _context(torch.bfloat16)
+    want = [_plain_for(wts, torch.bfloat16).latent_attention(x.double(), torch.arange(x.shape[0]), layer["mixer"], "m.", 1e-5) for x in hs]
+    sizes = [130, 1, 1, 62, 3, 16, 200]
+    run = _MixerRun(c, spec, wts)
+    calls = []
+    plain_call = c.ops._call
+    c.ops._call = lambda name, *a: (calls.append(name), plain_call(name, *a))[1]
+    try:
+        got = run.feed(hs, sizes)
+    finally:
+        c.ops._call = plain_call
+    fits = (d + dr + 63) // 64 * 64 <= 256 and (dv + 63) // 64 * 64 <= 128
+    assert (calls.count("hb_latent_scatter") == 4) == fits and (calls.count("hb_attention_sink_prefill") == 4) == fits
+    _assert_close(got, want, torch.bfloat16, "written out")
+    folded = _MixerRun(c, spec, wts)
+    folded.mixer.write_out = False
+    ref = folded.feed(hs, sizes)
+    for a, b in zip(got, ref):
+        assert (a - b).abs().max() < 2e-2 * max(1.0, b.abs().max().item())
+
+
+@pytest.mark.gpu
 def test_rotation_tables_with_yarn():
     require_gpu()
     import types
@@ -457,7 +533,7 @@ def test_whole_prompts(models, name, dtype):
     reqs = _requests(cfg, [1, 2, 7, 70, 150], 100)
     steps, peak = tt.trace_whole(reqs)
     eng = _engine(folder, dtype, peak)
-    _compare(tt.run_in_process(eng, steps), _reference(plain[dtype], reqs), dtype, "whole")
+    _compare(tt.run_in_process(eng, steps), _reference(plain, reqs, dtype), dtype, "whole")
     assert all(g.pool.num_free == g.pool.size for g in eng.cache.groups) and eng.cache.slots.num_held == 0
 
 
@@ -480,7 +556,7 @@ def test_the_residual_stream_after_every_layer(models, name):
     seq = eng.open_sequence()
     eng.step_chunked([StepEntry(seq, toks, [len(toks) - 1])])
     eng.close_sequence(seq)
-    _, layers = plain["float32"].forward(toks, return_layers=True)
+    _, layers = plain["exact"].forward(toks, return_layers=True)
     assert len(seen) == len(cfg["layers"])
     for i, (got, want) in enumerate(zip(seen, layers)):
         assert (got - want).abs().max() < 1e-4 * max(1.0, want.abs().max().item()), f"layer {i} ({cfg['layers'][i]['type']})"
@@ -496,7 +572,7 @@ def test_prompt_then_tokens_one_by_one(models, name, dtype):
     reqs = _requests(cfg, [3, 60, 190], 200)
     steps, peak = tt.trace_tail(reqs, tail=75)
     eng = _engine(folder, dtype, peak)
-    _compare(tt.run_in_process(eng, steps), _reference(plain[dtype], reqs), dtype, "tail")
+    _compare(tt.run_in_process(eng, steps), _reference(plain, reqs, dtype), dtype, "tail")
     assert eng.graph_replays > 0
 
 
@@ -515,7 +591,7 @@ def test_prompts_in_portions(models, name, dtype):
                       "end": ["p"] if at + n == len(toks) else []})
         at += n
     assert at == len(toks)
-    ref = _reference(plain[dtype], {"p": toks})
+    ref = _reference(plain, {"p": toks}, dtype)
     _compare(tt.run_in_process(_engine(folder, dtype, 192), steps), ref, dtype, "portions")
     whole = [{"step": 0, "entries": [{"id": "p", "tokens": toks, "want": list(range(len(toks)))}], "end": ["p"]}]
     _compare(tt.run_in_process(_engine(folder, dtype, 192, max_step_tokens=48), whole), ref, dtype, "cut by the engine")
@@ -533,7 +609,7 @@ def test_unequal_batches_with_slots_and_pages_used_again(models, name, dtype):
     steps, peak = tt.trace_batches(batches)
     eng = _engine(folder, dtype, peak)
     reqs = {rid: t for b in batches for rid, (t, _) in b.items()}
-    _compare(tt.run_in_process(eng, steps), _reference(plain[dtype], reqs), dtype, "batches")
+    _compare(tt.run_in_process(eng, steps), _reference(plain, reqs, dtype), dtype, "batches")
     assert eng.graph_replays > 0
     assert all(g.pool.num_free == g.pool.size for g in eng.cache.groups) and eng.cache.slots.num_held == 0
 
@@ -552,7 +628,7 @@ def test_long_decoding(models, name):
                       "end": ["l"] if p == len(toks) - 1 else []})
     eng = _engine(folder, "float32", 512)
     got = tt.run_in_process(eng, steps)
-    ref = _reference(plain["float32"], {"l": toks})
+    ref = _reference(plain, {"l": toks}, "float32")
     _compare(got, {k: ref[k] for k in got}, "float32", "long decoding")
     assert eng.graph_replays > 400
 
@@ -575,7 +651,7 @@ def test_greedy_generation_through_the_library(models, name):
     llm = hb.load(folder, dtype="float32", max_tokens=64 * 8, max_batch=3)       # two batches: slots are used again
     res = llm.generate(prompts, max_new_tokens=10, stop_token_ids=[])
     for r, p in zip(res, prompts):
-        assert r.tokens == _greedy(plain["float32"], p, 10), f"prompt of {len(p)} tokens"
+        assert r.tokens == _greedy(plain["exact"], p, 10), f"prompt of {len(p)} tokens"
     assert llm.generator.stats.batches == 2
     assert all(g.pool.num_free == g.pool.size for g in llm.engine.cache.groups)
 
@@ -588,6 +664,6 @@ def test_replay_program(models, tmp_path):
     steps, peak = tt.trace_batches(batches, want_all=False)
     reqs = {rid: t for rid, (t, _) in batches[0].items()}
     for dtype in DTYPES:
-        ref = _reference(plain[dtype], reqs)
+        ref = _reference(plain, reqs, dtype)
         got = tt.run_program(folder, dtype, steps, peak, str(tmp_path / dtype), cfg["vocab"])
         _compare(got, {k: ref[k] for k in got}, dtype, "trace_run")
