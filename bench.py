@@ -650,7 +650,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--shape", choices=("8b", "3b", "1b"), default="8b",
-                    help="layer sizes of the steady-decode line and of --timeline (default: the 8B shape of the contract)")
+                    help="layer sizes of the steady-decode line and of --timeline (default: the 8B shape of the default line)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each sequence's cache holds while decoding")
     ap.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16",
                     help="float32: the true 32-bit path (FP32-pipe products, general attention), a line of its own; "

@@ -18,7 +18,7 @@ def latent(heads, dim, rot_dim, vdim, rank, base=10000.0, scaling=None, scale=No
                                                   "scale": scale if scale is not None else (dim + rot_dim) ** -0.5, "rot": rot}}
 
 
-def parallel(left, right, left_scale=1.2, right_scale=0.9):
+def parallel(left, right, left_scale=1.25, right_scale=0.8):
     heads, kv_heads, dim, vdim, size, rot = left
     h2, d2, dv2, decay, rot2 = right
     return {"type": "parallel", "mixer": {
