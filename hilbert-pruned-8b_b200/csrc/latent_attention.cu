@@ -220,15 +220,15 @@ extern "C" int hb_latent_scatter(const void* kv, long long ldkv, const void* k_c
 }
 
 // ------------------------------------------------------------------------------------------------ head_linear
-// One block: 16 tokens x 64 output columns of one head.  A thread owns two neighbouring columns (one 4- or 8-byte
-// weight load serves both) and every eighth of the input features, for all 16 tokens; the eight partial sums of an
-// output are then added in a fixed order.  A decode step, whose few tokens give few blocks, so has eight warps reading
-// different weight rows at once instead of one thread walking all of a column's rows.
+// One block: 16 tokens x COLS output columns of one head (COLS 64, or 32 where 64 would leave most SMs without a block).
+// A thread owns two neighbouring columns (one 4- or 8-byte weight load serves both) and every SLICES-th input feature,
+// for all 16 tokens; the SLICES partial sums of an output are then added in a fixed order.  A decode step, whose few
+// tokens give few blocks, so has many threads reading different weight rows at once instead of one thread walking all
+// of a column's rows.  COLS is chosen from the sizes of the product alone, never from the number of tokens, so that a
+// token's result does not depend on what else the step brings.
 #define HL_TOKENS 16
-#define HL_COLS 64
 #define HL_KC 256            // input features staged at a time
-#define HL_SLICES 8
-#define HL_THREADS 256       // HL_COLS / 2 column pairs x HL_SLICES slices of the input features
+#define HL_THREADS 256       // COLS / 2 column pairs x SLICES slices of the input features
 
 template <typename TW> struct hl_pair;
 template <> struct hl_pair<bf16> {
@@ -238,11 +238,12 @@ template <> struct hl_pair<float> {
     static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
 };
 
-template <typename TW, typename TO>
+template <typename TW, typename TO, int HL_COLS>
 __global__ void __launch_bounds__(HL_THREADS)
 head_linear_kernel(const float* __restrict__ in, long long ldi, long long in_head, const TW* __restrict__ w, TO* __restrict__ out,
                    long long ldo, long long out_head, const float* __restrict__ gate, long long ldg, int n_tokens, int n_in, int n_out,
                    int pairs_aligned) {
+    constexpr int HL_SLICES = 2 * HL_THREADS / HL_COLS;
     pdl_trigger();
     // the staged inputs [HL_TOKENS][HL_KC + 1]; afterwards the partial sums [HL_SLICES][HL_TOKENS][HL_COLS]
     __shared__ float sh[HL_SLICES * HL_TOKENS * HL_COLS];
@@ -267,7 +268,7 @@ head_linear_kernel(const float* __restrict__ in, long long ldi, long long in_hea
         }
         __syncthreads();
         if (live0) {
-#pragma unroll 4
+#pragma unroll 8
             for (int k = slice; k < kc; k += HL_SLICES) {
                 const TW* wr = wh + (size_t)(k0 + k) * n_out + col;
                 float2 wv;
@@ -304,14 +305,22 @@ extern "C" int hb_head_linear(const float* in, long long ldi, long long in_head,
                               int n_out, void* stream) {
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && n_heads > 0 && n_heads <= 65535 && n_in > 0 && n_out > 0, "head_linear: bad sizes");
-    HB_REQUIRE((n_out + HL_COLS - 1) / HL_COLS <= 65535, "head_linear: too many output columns");
-    dim3 grid((n_tokens + HL_TOKENS - 1) / HL_TOKENS, n_heads, (n_out + HL_COLS - 1) / HL_COLS);
+    HB_REQUIRE((n_out + 31) / 32 <= 65535, "head_linear: too many output columns");
+    // narrow tiles where wide ones would not fill the SMs once (a matter of the product's sizes only)
+    const int cols = ((long long)n_heads * ((n_out + 63) / 64) < 148) ? 32 : 64;
+    dim3 grid((n_tokens + HL_TOKENS - 1) / HL_TOKENS, n_heads, (n_out + cols - 1) / cols);
     cudaStream_t s = (cudaStream_t)stream;
     // two neighbouring weights in one load: every row of every head must start on a pair's boundary
     const int pairs_aligned = (n_out % 2 == 0 && ((uintptr_t)w & 7) == 0) ? 1 : 0;
 #define HB_HL(TW, TO)                                                                                                              \
-    hb_launch(head_linear_kernel<TW, TO>, dim3(grid), dim3(HL_THREADS), 0, s, in, ldi, in_head, (const TW*)w, (TO*)out, ldo, out_head, gate, \
-              ldg, n_tokens, n_in, n_out, pairs_aligned)
+    do {                                                                                                                           \
+        if (cols == 32)                                                                                                            \
+            hb_launch(head_linear_kernel<TW, TO, 32>, dim3(grid), dim3(HL_THREADS), 0, s, in, ldi, in_head, (const TW*)w, (TO*)out, ldo, \
+                      out_head, gate, ldg, n_tokens, n_in, n_out, pairs_aligned);                                                   \
+        else                                                                                                                       \
+            hb_launch(head_linear_kernel<TW, TO, 64>, dim3(grid), dim3(HL_THREADS), 0, s, in, ldi, in_head, (const TW*)w, (TO*)out, ldo, \
+                      out_head, gate, ldg, n_tokens, n_in, n_out, pairs_aligned);                                                   \
+    } while (0)
     if (w_dtype == HB_BF16 && out_dtype == HB_BF16) HB_HL(bf16, bf16);
     else if (w_dtype == HB_BF16 && out_dtype == HB_F32) HB_HL(bf16, float);
     else if (w_dtype == HB_F32 && out_dtype == HB_F32) HB_HL(float, float);
