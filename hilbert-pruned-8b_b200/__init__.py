@@ -7,10 +7,10 @@ and hand-written sm_100a CUDA kernels underneath.  The GPU is required to run a 
 describing one (configuration, weight table, cache bookkeeping) needs none.
 """
 from . import cache, config, engine, parts, weights  # noqa: F401
-from .config import LlamaConfig, PogezenConfig, TonovikConfig, VuladraConfig, load_config, register_architecture
+from .config import LlamaConfig, MoponexConfig, PogezenConfig, TonovikConfig, VuladraConfig, load_config, register_architecture
 
 __version__ = "0.1.0"
-__all__ = ["cache", "config", "engine", "parts", "weights", "LlamaConfig", "PogezenConfig", "VuladraConfig", "TonovikConfig", "load_config", "register_architecture"]
+__all__ = ["cache", "config", "engine", "parts", "weights", "LlamaConfig", "PogezenConfig", "VuladraConfig", "TonovikConfig", "MoponexConfig", "load_config", "register_architecture"]
 
 
 def load(model: str, dtype: str = "bfloat16", max_tokens: int = 4096, device: int = 0, **kw):

@@ -73,5 +73,21 @@ def config_class_for(root: Dict[str, Any]) -> Any:
 def load_config(model_dir: str) -> Any:
     """Reads ``model_dir/config.json`` and returns the typed configuration of its architecture."""
     root = read_config_json(model_dir)
-    return config_class_for(root).from_dict(root)
+    config = config_class_for(root).from_dict(root)
+    if hasattr(config, "with_tensor_shapes"):
+        # an architecture may leave a size to a tensor's shape: it then gets the shapes the folder's headers state
+        config = config.with_tensor_shapes(_folder_shapes(model_dir))
+    return config
+
+
+def _folder_shapes(model_dir: str) -> Dict[str, Any]:
+    from ..weights.safetensors_io import SafetensorsFolder
+    try:
+        folder = SafetensorsFolder(model_dir)
+    except (OSError, ValueError):
+        return {}
+    try:
+        return {n: tuple(folder.entry(n).shape) for n in folder.names()}
+    finally:
+        folder.close()
 

@@ -43,6 +43,7 @@ class LayerSpec:
     parts: Dict[str, PartSpec]
     part_prefixes: Dict[str, str]
     block: str = "prenorm"
+    block_params: Dict[str, Any] = field(default_factory=dict)      # constants of the arrangement itself (a factor on the sublayers' results)
 
     def part(self, role: str) -> PartSpec:
         if role not in self.parts:
@@ -57,10 +58,10 @@ class LayerSpec:
         """A copy with the part in ``role`` replaced (or added) and, if given, its tensor prefix."""
         parts = {**self.parts, role: spec}
         prefixes = dict(self.part_prefixes) if prefix is None else {**self.part_prefixes, role: prefix}
-        return LayerSpec(self.prefix, parts, prefixes, self.block)
+        return LayerSpec(self.prefix, parts, prefixes, self.block, dict(self.block_params))
 
     def with_block(self, block: str) -> "LayerSpec":
-        return LayerSpec(self.prefix, dict(self.parts), dict(self.part_prefixes), block)
+        return LayerSpec(self.prefix, dict(self.parts), dict(self.part_prefixes), block, dict(self.block_params))
 
     # the two roles most layers have, by name (a block without one of them raises KeyError)
     @property

@@ -110,12 +110,12 @@ int hb_qkv_prepare(const void* proj, int proj_dtype, long long ldp, const float*
                    int n_heads, int n_kv_heads, int head_dim, int v_dim, int unit_norm, const float* q_norm_w, const float* k_norm_w,
                    float eps, void* q_out, int q_dtype, long long ldq, void* k_cache, void* v_cache, int cache_dtype, const int* page_table, int pt_width,
                    const int* tok_seq, const int* positions, int n_tokens, int n_pages, int append, const float* v_lambda,
-                   float* v_first, int v_mode, int* status, void* stream);
+                   float* v_first, int v_mode, int interleaved, int v_from_k, int* status, void* stream);
 // out [tokens][heads][all_values ? kv heads : 1][v_dim] float32
 int hb_attention_sink(const void* q, int q_dtype, long long ldq, const void* k_cache, const void* v_cache, int cache_dtype,
                       const int* page_table, int pt_width, const int* tok_seq, const int* positions, float* out, int n_tokens,
-                      int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first,
-                      int all_values, int n_pages, int* status, void* stream);
+                      int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first, int chunk,
+                      const float* sink, int all_values, int n_pages, int* status, void* stream);
 int hb_head_mix(const float* partial, const float* mix, void* out, int out_dtype, long long ldo, int n_tokens, int n_heads,
                 int n_kv_heads, int v_dim, int n_val, int ones, const float* gate, long long ldg, void* stream);
 // One block per (token, key split) for all heads; see attention_sink.cu.  hb_attention_heads_variant: 0 when the sizes are not built.
@@ -124,8 +124,8 @@ int hb_attention_heads_writes_output(int n_heads, int n_kv_heads, int head_dim, 
 int hb_attention_heads(const void* q, int q_dtype, long long ldq, const void* k_cache, const void* v_cache, int cache_dtype,
                        const int* page_table, int pt_width, const int* tok_seq, const int* positions, float* partial, float* ml,
                        const float* mix, void* out, long long ldo, int ones, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                       int v_dim, float scale, int window, int keep_first, int splits, int n_pages, int allow_mma, int* status,
-                       void* stream);
+                       int v_dim, float scale, int window, int keep_first, int chunk, const float* sink, int splits, int n_pages,
+                       int allow_mma, int* status, void* stream);
 int hb_head_mix_splits(const float* partial, const float* ml, const float* mix, void* out, int out_dtype, long long ldo, int n_tokens,
                        int n_heads, int n_kv_heads, int v_dim, int splits, int ones, const float* gate, long long ldg, void* stream);
 // Flash-style on the tensor cores for steps of many tokens (bfloat16, head sizes 64 or 128); out float32
@@ -134,7 +134,7 @@ int hb_attention_sink_prefill_supported(int n_heads, int n_kv_heads, int head_di
 int hb_attention_sink_prefill(const void* q, long long q_stride, const void* k_cache, const void* v_cache, const int* page_table,
                               int pt_width, const int* seq_start, const int* seq_pos0, float* out, int n_seqs, int q_blocks,
                               int n_heads, int n_kv_heads, int head_dim, int v_dim, int n_val, float scale, int window,
-                              int keep_first, int n_pages, int* status, void* stream);
+                              int keep_first, int chunk, const float* sink, int n_pages, int* status, void* stream);
 // proj rows: [q heads*d | k heads*d | v heads*dv | gate heads*dv | z_i heads | z_f heads]; state per slot:
 // S [heads][d][dv], n [heads][d], m [heads]; out [tokens][heads*dv] float32
 int hb_mlstm_scan(const void* proj, int proj_dtype, long long ldp, const float* gate_bias, float cap, float q_scale, float* state,
@@ -236,10 +236,37 @@ int hb_moe_glu(const void* h, int h_dtype, long long ldh, const void* w_gate, co
                float limit, float alpha, int tensor_cores, void* stream);
 int hb_moe_down(const void* act, int act_dtype, long long lda, const void* w_down, int w_dtype, const int* offsets, const int* order,
                 const int* tiles, int max_tiles, int top, float* down, long long ldd, int width, int ff, int tensor_cores, void* stream);
+// experts non-null: entries whose expert number is n_real or more are identity experts (their result is the row of h)
 int hb_moe_combine(const float* down, long long ldd, const float* weights, int top, float* out, long long ldo, int n_tokens, int width,
-                   int accumulate, void* stream);
+                   int accumulate, const int* experts, int n_real, const void* h, int h_dtype, long long ldh, void* stream);
 int hb_glu_clamp(const float* in, long long ldi, void* out, int out_dtype, long long ldo, int n_rows, int F, float limit, float alpha,
                  void* stream);
+// softmax over all router outputs, choice by score + correction inside the `keep` best of `groups` runs, weights from the
+// scores divided by their sum + norm_eps
+int hb_moe_route_scores(const void* h, int h_dtype, long long ldh, const float* w_router, const float* correction, int* experts,
+                        float* weights, int n_tokens, int width, int n_outputs, int top, int groups, int keep, float norm_eps,
+                        void* stream);
+// kind 0: gelu_tanh(in[:, :F]) * in[:, F:2F]; kind 1: gelu_erf(in[:, :F]) * sigmoid(in[:, row_gate]) (row_gate < 0: no gate)
+int hb_gelu_unit(const float* in, long long ldi, void* out, int out_dtype, long long ldo, int n_rows, int F, int kind, int row_gate,
+                 void* stream);
+// Token embedding plus the hashed embedding of (previous token, token) (elementwise.cu); state: one int32 per slot
+int hb_embed_pair(const int* tokens, const void* table, int table_dtype, const void* pairs, float* out, int n_tokens, int hidden,
+                  int vocab, int packed, float scale, int buckets, long long mul_prev, long long mul_cur, const int* positions,
+                  const int* tok_seq, const int* seq_start, const int* state_slots, int* state, long long state_stride, int* status,
+                  void* stream);
+// x += m * y, optionally followed by the next norm of the new rows; out (+)= norm(a) wa + norm(b) wb (post_norm.cu)
+int hb_scaled_add_norm(const float* y, long long ldy, float m, float* x, long long ldx, const float* w2, float eps2, float offset2,
+                       void* h, int h_dtype, long long ldh, int n_rows, int n, void* stream);
+int hb_normed_sum(const float* a, long long lda, const float* wa, const float* b, long long ldb, const float* wb, float eps, float* out,
+                  long long ldo, int n_rows, int n, int accumulate, void* stream);
+// The recurrent memory per head with token-dependent decay (head_scan.cu): decay_mode 0 one scalar per (token, head) from a
+// step size, 1 one per (token, head, state index) from a sigmoid; chunk_len 0: one block walks a sequence's tokens, else
+// three launches with carry of n_seqs * max_chunks * heads * (2 * head_dim * n_state + (mode ? n_state : 1)) floats
+int hb_head_scan(const float* u, long long ldu, const float* kmat, long long ldk, const float* qmat, long long ldq, const float* z,
+                 long long ldz, const float* draw, long long ldd, const float* dbias, const float* a_log, float inv_tau,
+                 const float* dskip, float q_scale, float* state, long long state_stride, const int* state_slots, const int* seq_start,
+                 void* out, int out_dtype, long long ldo, int n_seqs, int n_heads, int n_groups, int head_dim, int n_state,
+                 int decay_mode, int chunk_len, int max_chunks, float* carry, long long carry_floats, void* stream);
 
 #ifdef __cplusplus
 }

@@ -28,7 +28,8 @@ qkv_prepare_kernel(const TP* __restrict__ proj, long long ldp, const float* __re
                    const float* __restrict__ k_norm_w, float eps, TQ* __restrict__ q_out, long long ldq,
                    TC* __restrict__ k_cache, TC* __restrict__ v_cache, const int* __restrict__ page_table, int pt_width,
                    const int* __restrict__ tok_seq, const int* __restrict__ positions, int n_pages, int append,
-                   const float* __restrict__ v_lambda, float* __restrict__ v_first, int v_mode, int* status) {
+                   const float* __restrict__ v_lambda, float* __restrict__ v_first, int v_mode, int interleaved, int v_from_k,
+                   int* status) {
     pdl_trigger();
     __shared__ float xs[QP_MAX_HD];
     __shared__ float scratch[33];
@@ -67,11 +68,12 @@ qkv_prepare_kernel(const TP* __restrict__ proj, long long ldp, const float* __re
         for (int d = tid; d < hd; d += QP_THREADS) {
             float y = xs[d];
             if (d < rot) {
-                const int i = d < half ? d : d - half;
+                // pair i is (i, i + rot/2), or with `interleaved` (2i, 2i + 1)
+                const int i = interleaved ? d >> 1 : (d < half ? d : d - half);
                 const float2 cs = table[(size_t)t * half + i];
                 float y1, y2;
-                rope_pair(xs[i], xs[i + half], cs.x, cs.y, y1, y2);
-                y = d < half ? y1 : y2;
+                rope_pair(xs[interleaved ? 2 * i : i], xs[interleaved ? 2 * i + 1 : i + half], cs.x, cs.y, y1, y2);
+                y = (interleaved ? (d & 1) == 0 : d < half) ? y1 : y2;
             }
             ss = fmaf(y, y, ss);
         }
@@ -84,19 +86,21 @@ qkv_prepare_kernel(const TP* __restrict__ proj, long long ldp, const float* __re
         for (int d = tid; d < hd; d += QP_THREADS) {
             float y = xs[d];
             if (d < rot) {
-                const int i = d < half ? d : d - half;
+                // pair i is (i, i + rot/2), or with `interleaved` (2i, 2i + 1)
+                const int i = interleaved ? d >> 1 : (d < half ? d : d - half);
                 const float2 cs = table[(size_t)t * half + i];
                 float y1, y2;
-                rope_pair(xs[i], xs[i + half], cs.x, cs.y, y1, y2);
-                y = d < half ? y1 : y2;
+                rope_pair(xs[interleaved ? 2 * i : i], xs[interleaved ? 2 * i + 1 : i + half], cs.x, cs.y, y1, y2);
+                y = (interleaved ? (d & 1) == 0 : d < half) ? y1 : y2;
             }
             y *= inv;
             if (is_q) q_out[(size_t)t * ldq + col0 + d] = from_f32<TQ>(y);
             else if (append && page >= 0) k_cache[cache_offset(page, slot - nh, pos, nkv, hd) + d] = from_f32<TC>(y);
         }
     } else {
+        // the values: a projection of their own, or (`v_from_k`) the keys as projected, before their norm and rotation
         const int g = slot - nh - nkv;
-        const int col0 = (nh + nkv) * hd + g * vd;
+        const int col0 = v_from_k ? nh * hd + g * hd : (nh + nkv) * hd + g * vd;
         const TP* row = proj + (size_t)t * ldp + col0;
         const float lam = v_mode == 2 ? v_lambda[0] : 0.0f;
         float* vf = v_first ? pdl_fresh(v_first) + (size_t)t * nkv * vd + (size_t)g * vd : nullptr;
@@ -113,9 +117,11 @@ extern "C" int hb_qkv_prepare(const void* proj, int proj_dtype, long long ldp, c
                               int n_heads, int n_kv_heads, int head_dim, int v_dim, int unit_norm, const float* q_norm_w,
                               const float* k_norm_w, float eps, void* q_out, int q_dtype, long long ldq, void* k_cache, void* v_cache, int cache_dtype, const int* page_table,
                               int pt_width, const int* tok_seq, const int* positions, int n_tokens, int n_pages, int append,
-                              const float* v_lambda, float* v_first, int v_mode, int* status, void* stream) {
+                              const float* v_lambda, float* v_first, int v_mode, int interleaved, int v_from_k, int* status,
+                              void* stream) {
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0 && v_dim > 0, "qkv_prepare: bad sizes");
+    HB_REQUIRE(!v_from_k || v_dim == head_dim, "qkv_prepare: values that are the keys have the keys' size");
     HB_REQUIRE(head_dim <= QP_MAX_HD, "qkv_prepare: head size %d is larger than %d", head_dim, QP_MAX_HD);
     HB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= head_dim, "qkv_prepare: %d rotated dimensions of %d", rot, head_dim);
     HB_REQUIRE(rot == 0 || table != nullptr, "qkv_prepare: no rotation table");
@@ -131,7 +137,7 @@ extern "C" int hb_qkv_prepare(const void* proj, int proj_dtype, long long ldp, c
 #define HB_QP_LAUNCH(TP, TQ)                                                                                                   \
     hb_launch(qkv_prepare_kernel<TP, TQ, TQ>, dim3(grid), dim3(QP_THREADS), 0, s, (const TP*)proj, ldp, bias, (const float2*)table, rot,  \
               n_heads, n_kv_heads, head_dim, v_dim, unit_norm, q_norm_w, k_norm_w, eps, (TQ*)q_out, ldq, (TQ*)k_cache, (TQ*)v_cache, page_table,       \
-              pt_width, tok_seq, positions, n_pages, append, v_lambda, v_first, v_mode, status)
+              pt_width, tok_seq, positions, n_pages, append, v_lambda, v_first, v_mode, interleaved, v_from_k, status)
     if (proj_dtype == HB_F32 && q_dtype == HB_F32) HB_QP_LAUNCH(float, float);
     else if (proj_dtype == HB_F32 && q_dtype == HB_BF16) HB_QP_LAUNCH(float, bf16);
     else if (proj_dtype == HB_BF16 && q_dtype == HB_BF16) HB_QP_LAUNCH(bf16, bf16);
@@ -150,7 +156,7 @@ __global__ void __launch_bounds__(AS_THREADS)
 attention_sink_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                       const int* __restrict__ page_table, int pt_width, const int* __restrict__ tok_seq,
                       const int* __restrict__ positions, float* __restrict__ out, int nh, int nkv, int hd, int vd, float scale,
-                      int window, int keep_first, int all_values, int n_pages, int* status) {
+                      int window, int keep_first, int chunk, const float* __restrict__ sink, int all_values, int n_pages, int* status) {
     pdl_trigger();
     pdl_wait();
     q = pdl_fresh(q);
@@ -166,7 +172,7 @@ attention_sink_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
     const int p = positions[t];
     const int* pt = page_table + (size_t)tok_seq[t] * pt_width;
     // the keys this query sees: [0, kept) and [lo, p]
-    const int lo_w = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int lo_w = hb_oldest_visible(p, window, chunk);
     const int kept = min(min(keep_first, lo_w), p + 1);
     const int lo = max(lo_w, kept);
     const int total = kept + (p - lo + 1);
@@ -176,7 +182,8 @@ attention_sink_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
 
     const int n_val = all_values ? nkv : 1;
     const int n_out = n_val * vd;
-    float m = -INFINITY, l = 0.0f;
+    // a sink is one more term exp(sink[j]) of the softmax's sum, with no value: the running maximum and sum start from it
+    float m = sink ? sink[j] : -INFINITY, l = sink ? 1.0f : 0.0f;
     float acc[AS_MAX_ACC];
 #pragma unroll
     for (int i = 0; i < AS_MAX_ACC; i++) acc[i] = 0.0f;
@@ -237,21 +244,22 @@ attention_sink_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
 extern "C" int hb_attention_sink(const void* q, int q_dtype, long long ldq, const void* k_cache, const void* v_cache,
                                  int cache_dtype, const int* page_table, int pt_width, const int* tok_seq,
                                  const int* positions, float* out, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                 int v_dim, float scale, int window, int keep_first, int all_values, int n_pages,
-                                 int* status, void* stream) {
+                                 int v_dim, float scale, int window, int keep_first, int chunk, const float* sink, int all_values,
+                                 int n_pages, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0 && v_dim > 0 && n_pages > 0, "attention: bad sizes");
     HB_REQUIRE(n_heads % n_kv_heads == 0, "attention: %d heads are no multiple of %d kv heads", n_heads, n_kv_heads);
     HB_REQUIRE(head_dim <= AS_MAX_HD, "attention: head size %d is larger than %d", head_dim, AS_MAX_HD);
     HB_REQUIRE((all_values ? n_kv_heads : 1) * v_dim <= AS_THREADS * AS_MAX_ACC,
                "attention: %d value columns per query head are more than %d", (all_values ? n_kv_heads : 1) * v_dim, AS_THREADS * AS_MAX_ACC);
-    HB_REQUIRE(n_heads <= 65535 && window >= 0 && keep_first >= 0, "attention: bad head count, window or kept tokens");
+    HB_REQUIRE(n_heads <= 65535 && window >= 0 && keep_first >= 0 && chunk >= 0, "attention: bad head count, window or kept tokens");
+    HB_REQUIRE(chunk == 0 || (window == 0 && keep_first == 0), "attention: chunks come without a window and kept first tokens");
     dim3 grid(n_tokens, n_heads);
     cudaStream_t s = (cudaStream_t)stream;
 #define HB_AS_LAUNCH(TQ, TC)                                                                                                  \
     hb_launch(attention_sink_kernel<TQ, TC>, dim3(grid), dim3(AS_THREADS), 0, s, (const TQ*)q, ldq, (const TC*)k_cache, (const TC*)v_cache, \
               page_table, pt_width, tok_seq, positions, out, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first,      \
-              all_values, n_pages, status)
+              chunk, sink, all_values, n_pages, status)
     if (q_dtype == HB_F32 && cache_dtype == HB_F32) HB_AS_LAUNCH(float, float);
     else if (q_dtype == HB_BF16 && cache_dtype == HB_BF16) HB_AS_LAUNCH(bf16, bf16);
     else return hb_fail("attention: unsupported dtypes q %d cache %d", q_dtype, cache_dtype);
@@ -332,7 +340,8 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
                        const int* __restrict__ page_table, int pt_width, const int* __restrict__ tok_seq,
                        const int* __restrict__ positions, float* __restrict__ partial, float* __restrict__ ml,
                        const float* __restrict__ mix, TO* __restrict__ out, long long ldo, int ones, int nh, int nkv, int hd,
-                       int vd, float scale, int window, int keep_first, int splits, int n_pages, int* status) {
+                       int vd, float scale, int window, int keep_first, int chunk, const float* __restrict__ sink, int splits,
+                       int n_pages, int* status) {
     pdl_trigger();
     constexpr int CE = 16 / (int)sizeof(TC);            // cache elements per 16-byte piece
     extern __shared__ __align__(16) unsigned char ah_smem[];
@@ -353,7 +362,7 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
     const int t = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int p = positions[t];
     const int* pt = page_table + (size_t)tok_seq[t] * pt_width;
-    const int lo_w = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int lo_w = hb_oldest_visible(p, window, chunk);
     const int kept = min(min(keep_first, lo_w), p + 1);
     const int lo = max(lo_w, kept);
     const int total = kept + (p - lo + 1);
@@ -389,8 +398,10 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
     v_cache = pdl_fresh(v_cache);
     for (int i = tid; i < nh * hd; i += AH_THREADS) qs[i] = to_f32(q[(size_t)t * ldq + i]);
     for (int i = tid; i < nh; i += AH_THREADS) {
-        m_s[i] = -INFINITY;
-        l_s[i] = 0.0f;
+        // a sink (one more term exp(sink[i]) of the sum, with no value) is where the first split's running maximum and sum start
+        const bool with_sink = sink != nullptr && split == 0;
+        m_s[i] = with_sink ? sink[i] : -INFINITY;
+        l_s[i] = with_sink ? 1.0f : 0.0f;
     }
     const int kcpr = hd / CE, vcpr = vd / CE;            // 16-byte pieces per key row and per value row
     for (int v0 = v_begin; v0 < v_end; v0 += KT) {
@@ -722,7 +733,7 @@ template <typename TQ, typename TC, typename TO, int HPT, int KT, bool MMA>
 static int ah_launch(dim3 grid, size_t smem, cudaStream_t s, const void* q, long long ldq, const void* k_cache, const void* v_cache,
                      const int* page_table, int pt_width, const int* tok_seq, const int* positions, float* partial, float* ml,
                      const float* mix, void* out, long long ldo, int ones, int nh, int nkv, int hd, int vd, float scale, int window,
-                     int keep_first, int splits, int n_pages, int* status) {
+                     int keep_first, int chunk, const float* sink, int splits, int n_pages, int* status) {
     static bool done[HB_MAX_DEVICES];
     if (!done[hb_device_slot()]) {
         cudaError_t e = cudaFuncSetAttribute(attention_heads_kernel<TQ, TC, TO, HPT, KT, MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -731,7 +742,7 @@ static int ah_launch(dim3 grid, size_t smem, cudaStream_t s, const void* q, long
     }
     hb_launch(attention_heads_kernel<TQ, TC, TO, HPT, KT, MMA>, dim3(grid), dim3(AH_THREADS), smem, s, (const TQ*)q, ldq, (const TC*)k_cache,
               (const TC*)v_cache, page_table, pt_width, tok_seq, positions, partial, ml, mix, (TO*)out, ldo, ones, nh, nkv, hd, vd, scale,
-              window, keep_first, splits, n_pages, status);
+              window, keep_first, chunk, sink, splits, n_pages, status);
     return hb_check_launch("attention_heads");
 }
 
@@ -740,13 +751,14 @@ static int ah_launch(dim3 grid, size_t smem, cudaStream_t s, const void* q, long
 extern "C" int hb_attention_heads(const void* q, int q_dtype, long long ldq, const void* k_cache, const void* v_cache, int cache_dtype,
                                   const int* page_table, int pt_width, const int* tok_seq, const int* positions, float* partial,
                                   float* ml, const float* mix, void* out, long long ldo, int ones, int n_tokens, int n_heads,
-                                  int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first, int splits,
-                                  int n_pages, int allow_mma, int* status, void* stream) {
+                                  int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first, int chunk,
+                                  const float* sink, int splits, int n_pages, int allow_mma, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     const int variant = hb_attention_heads_variant(n_heads, n_kv_heads, head_dim, v_dim, cache_dtype, allow_mma);
     HB_REQUIRE(variant != 0, "attention_heads: these head sizes are not built");
     HB_REQUIRE(q_dtype == cache_dtype, "attention_heads: queries and cache must have one dtype");
-    HB_REQUIRE(splits >= 1 && splits <= 65535 && window >= 0 && keep_first >= 0 && n_pages > 0, "attention_heads: bad sizes");
+    HB_REQUIRE(splits >= 1 && splits <= 65535 && window >= 0 && keep_first >= 0 && chunk >= 0 && n_pages > 0, "attention_heads: bad sizes");
+    HB_REQUIRE(chunk == 0 || (window == 0 && keep_first == 0), "attention_heads: chunks come without a window and kept first tokens");
     const bool whole = hb_attention_heads_writes_output(n_heads, n_kv_heads, head_dim, v_dim, cache_dtype, allow_mma) != 0;
     HB_REQUIRE(out == nullptr || (splits == 1 && whole), "attention_heads: the block writes the output only with one split and every head in one thread");
     HB_REQUIRE(out != nullptr || (partial != nullptr && ml != nullptr), "attention_heads: no place for the partial results");
@@ -756,7 +768,7 @@ extern "C" int hb_attention_heads(const void* q, int q_dtype, long long ldq, con
     cudaStream_t s = (cudaStream_t)stream;
 #define HB_AH(TQ, TO, HPT, KT, MMA)                                                                                                \
     return ah_launch<TQ, TQ, TO, HPT, KT, MMA>(grid, smem, s, q, ldq, k_cache, v_cache, page_table, pt_width, tok_seq, positions, partial, ml,  \
-                                          mix, out, ldo, ones, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first, splits,  \
+                                          mix, out, ldo, ones, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first, chunk, sink, splits,  \
                                           n_pages, status)
     if (bf) { if (variant == AH_VARIANT_MMA) HB_AH(bf16, bf16, 1, 32, true); else if (variant == 4) HB_AH(bf16, bf16, 4, 32, false); else HB_AH(bf16, bf16, 32, 32, false); }
     else { if (variant == 4) HB_AH(float, float, 4, 16, false); else HB_AH(float, float, 32, 16, false); }

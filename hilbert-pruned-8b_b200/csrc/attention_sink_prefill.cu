@@ -8,7 +8,8 @@
 // index of its own and the scores are made once per value head; without mixing the grid has one value
 // head per query head, its own.  Keys are walked page by page (64 keys) through a cp.async pipeline:
 // first the pages of the kept first tokens that lie before the window, then the window's pages.  Query
-// row at position p sees key s if s <= p and (p - s < window or s < keep_first).  Scores, running
+// row at position p sees key s if s <= p and (p - s < window or s < keep_first); with `chunk` instead, if s lies in p's
+// own run of `chunk` positions.  `sink_logit` (per head): one more term of the softmax's sum.  Scores, running
 // maximum and sum are float32.  The weights enter the second product as TWO bfloat16 terms, hi = bf16(w)
 // and lo = bf16(w - hi), added in the float32 accumulator: exact to 16 mantissa bits.  The result is
 // normalised and written in float32: out[token][head][value head (or 0)][v_dim].
@@ -35,7 +36,8 @@ __global__ void __launch_bounds__(SP_THREADS)
 attn_sink_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                          const int* __restrict__ page_table, int pt_width, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_pos0, float* __restrict__ out, int n_seqs, int nh, int nkv, int n_val,
-                         float scale_log2e, int window, int keep_first, int n_pages, int* status) {
+                         float scale_log2e, int window, int keep_first, int chunk, const float* __restrict__ sink_logit, int n_pages,
+                         int* status) {
     pdl_trigger();
     pdl_wait();
     q = pdl_fresh(q);
@@ -82,14 +84,14 @@ attn_sink_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const b
     // pages of the CTA: the window's, from the oldest key its first row sees to its last row's own key, and
     // before them the pages of kept first tokens that the window no longer covers
     const int first_pos = pos0 + row_base, last_pos = pos0 + row_base + rows_here - 1;
-    const int lo_cta = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+    const int lo_cta = hb_oldest_visible(first_pos, window, chunk);
     const int p_begin = lo_cta / HB_PAGE_TOKENS, p_end = last_pos / HB_PAGE_TOKENS + 1;
     const int n_sink = window > 0 ? min((keep_first + HB_PAGE_TOKENS - 1) / HB_PAGE_TOKENS, p_begin) : 0;
     const int n_iter = n_sink + (p_end - p_begin);
-    const int lo0 = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
-    const int lo1 = (window > 0 && p1 - window + 1 > 0) ? p1 - window + 1 : 0;
+    const int lo0 = hb_oldest_visible(p0, window, chunk);
+    const int lo1 = hb_oldest_visible(p1, window, chunk);
     const int w_first = pos0 + row_base + warp * 16, w_last = w_first + 15;
-    const int w_lo = (window > 0 && w_first - window + 1 > 0) ? w_first - window + 1 : 0;
+    const int w_lo = hb_oldest_visible(w_first, window, chunk);
 
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     bool bad_page = false;
@@ -118,6 +120,12 @@ attn_sink_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const b
 #pragma unroll
     for (int i = 0; i < VD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    if (sink_logit != nullptr) {
+        // one more term exp(sink) of every row's sum, with no value: the running maximum starts there, and one lane of the
+        // four that share a row carries the term in its part of the sum
+        m[0] = m[1] = sink_logit[head] * SP_LOG2E;
+        l[0] = l[1] = (lane & 3) == 0 ? 1.0f : 0.0f;
+    }
 
 #pragma unroll
     for (int s = 0; s < SP_STAGES - 1; s++) load_page(s, s);
@@ -147,7 +155,7 @@ attn_sink_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const b
                 mma_bf16_16816(s[2 * kq + 1], qf[ks], kf[2], kf[3]);
             }
         }
-        const bool edge = sink || page_last > w_first || page_first < ((window > 0) ? w_last - window + 1 : 0);
+        const bool edge = sink || page_last > w_first || page_first < hb_oldest_visible(w_last, window, chunk);
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < 8; nt++)
@@ -237,7 +245,8 @@ extern "C" int hb_attention_sink_prefill_supported(int n_heads, int n_kv_heads, 
 template <int HD, int VD>
 static int launch_sink_prefill(const void* q, long long q_stride, const void* kc, const void* vc, const int* page_table, int pt_width,
                                const int* seq_start, const int* seq_pos0, float* out, int n_seqs, int q_blocks, int nh, int nkv,
-                               int n_val, float scale, int window, int keep_first, int n_pages, int* status, cudaStream_t s) {
+                               int n_val, float scale, int window, int keep_first, int chunk, const float* sink, int n_pages, int* status,
+                               cudaStream_t s) {
     constexpr int SMEM = SP_STAGES * HB_PAGE_TOKENS * (HD + VD) * 2;
     static bool attr_done[HB_MAX_DEVICES] = {};
     bool& attr_set = attr_done[hb_device_slot()];
@@ -248,7 +257,7 @@ static int launch_sink_prefill(const void* q, long long q_stride, const void* kc
     }
     dim3 grid(nh, q_blocks, n_val);
     hb_launch(attn_sink_prefill_kernel<HD, VD>, dim3(grid), dim3(SP_THREADS), SMEM, s, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc,
-              page_table, pt_width, seq_start, seq_pos0, out, n_seqs, nh, nkv, n_val, scale * SP_LOG2E, window, keep_first, n_pages, status);
+              page_table, pt_width, seq_start, seq_pos0, out, n_seqs, nh, nkv, n_val, scale * SP_LOG2E, window, keep_first, chunk, sink, n_pages, status);
     return hb_check_launch("attention_sink_prefill");
 }
 
@@ -257,18 +266,20 @@ static int launch_sink_prefill(const void* q, long long q_stride, const void* kc
 extern "C" int hb_attention_sink_prefill(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
                                          const int* page_table, int pt_width, const int* seq_start, const int* seq_pos0,
                                          float* out, int n_seqs, int q_blocks, int n_heads, int n_kv_heads, int head_dim, int v_dim,
-                                         int n_val, float scale, int window, int keep_first, int n_pages, int* status, void* stream) {
+                                         int n_val, float scale, int window, int keep_first, int chunk, const float* sink, int n_pages, int* status,
+                                         void* stream) {
     if (n_seqs == 0 || q_blocks == 0) return 0;
     HB_REQUIRE(hb_attention_sink_prefill_supported(n_heads, n_kv_heads, head_dim, v_dim),
                "attention_sink_prefill: head sizes %d and %d are not built (keys 64 to 256 in steps of 64, values 64 or 128)", head_dim, v_dim);
-    HB_REQUIRE(n_seqs > 0 && q_blocks > 0 && q_blocks <= 65535 && window >= 0 && keep_first >= 0, "attention_sink_prefill: bad sizes");
+    HB_REQUIRE(n_seqs > 0 && q_blocks > 0 && q_blocks <= 65535 && window >= 0 && keep_first >= 0 && chunk >= 0, "attention_sink_prefill: bad sizes");
+    HB_REQUIRE(chunk == 0 || (window == 0 && keep_first == 0), "attention_sink_prefill: chunks come without a window and kept first tokens");
     HB_REQUIRE(n_val == 1 || (n_val == n_kv_heads && n_val <= 65535), "attention_sink_prefill: %d value heads per head, 1 or %d expected", n_val, n_kv_heads);
     HB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q & 3) == 0 && ((uintptr_t)out & 7) == 0, "attention_sink_prefill: queries and output must be aligned");
     HB_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0, "attention_sink_prefill: cache must be 16-byte aligned");
     cudaStream_t s = (cudaStream_t)stream;
 #define HB_SP(HD, VD)                                                                                                                     \
     return launch_sink_prefill<HD, VD>(q, q_stride, k_cache, v_cache, page_table, pt_width, seq_start, seq_pos0, out, n_seqs, q_blocks, n_heads, \
-                                       n_kv_heads, n_val, scale, window, keep_first, n_pages, status, s)
+                                       n_kv_heads, n_val, scale, window, keep_first, chunk, sink, n_pages, status, s)
     if (head_dim == 256 && v_dim == 128) HB_SP(256, 128);
     if (head_dim == 256 && v_dim == 64) HB_SP(256, 64);
     if (head_dim == 192 && v_dim == 128) HB_SP(192, 128);

@@ -266,6 +266,14 @@ __device__ __forceinline__ float silu_fast(float z) {
     return __fdividef(z, 1.0f + e);
 }
 
+// The oldest key a query at position p sees (kept first tokens aside): with a sliding window of `window` tokens
+// p - window + 1; with `chunk` > 0 the first position of p's own chunk (positions are cut into runs of `chunk`
+// from the sequence's start, and a query sees only its own run); 0 when neither is set.  Never decreases with p.
+__device__ __forceinline__ int hb_oldest_visible(int p, int window, int chunk) {
+    if (chunk > 0) return p - p % chunk;
+    return (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+}
+
 // Address of token position `pos` of kv head `g` in a paged cache layer
 // [pages][kv_heads][HB_PAGE_TOKENS][head_dim]; `page` is the physical page.
 __device__ __forceinline__ size_t cache_offset(int page, int g, int pos, int nkv, int hd) {

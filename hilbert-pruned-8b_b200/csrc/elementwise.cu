@@ -46,6 +46,77 @@ extern "C" int hb_embed(const int* tokens, const void* table, int table_dtype, f
     return hb_check_launch("embed");
 }
 
+// Token embedding plus a hashed embedding of the pair (previous token, token):
+//   x[t,:] = float(E[token[t],:]) * scale + float(Bg[row,:]),  row = (prev * mul_prev + token * mul_cur) mod buckets,
+// and for a sequence's first token (position 0) row = buckets, the table's last row.  The previous token of a step's
+// first token is the sequence's state (one int32 per slot), which the block of that token also brings up to date with
+// the sequence's last token of this step: no other block touches the slot.
+template <typename TW>
+__global__ void embed_pair_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, const TW* __restrict__ pairs,
+                                  float* __restrict__ out, int hidden, int vocab, int kbt, float scale, int buckets,
+                                  long long mul_prev, long long mul_cur, const int* __restrict__ positions,
+                                  const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                                  const int* __restrict__ state_slots, int* __restrict__ state, long long state_stride, int* status) {
+    pdl_trigger();
+    pdl_wait();
+    tokens = pdl_fresh(tokens);
+    state = pdl_fresh(state);
+    __shared__ int row_s;
+    const int t = blockIdx.x;
+    auto token_at = [&](int i) {
+        int tok = tokens[i];
+        if (tok < 0 || tok >= vocab) {
+            hb_note(status, HB_STATUS_TOKEN, 1 + i);
+            tok = 0;
+        }
+        return tok;
+    };
+    const int tok = token_at(t);
+    if (threadIdx.x == 0) {
+        const int b = tok_seq[t], first = seq_start[b];
+        int prev;
+        if (t == first) {
+            int* slot = state + (size_t)state_slots[b] * state_stride;
+            prev = *slot;
+            *slot = token_at(seq_start[b + 1] - 1);
+        } else {
+            prev = token_at(t - 1);
+        }
+        row_s = positions[t] == 0 ? buckets : (int)(((long long)prev * mul_prev + (long long)tok * mul_cur) % (long long)buckets);
+    }
+    __syncthreads();
+    const TW* prow = pairs + (size_t)row_s * hidden;
+    float* o = out + (size_t)t * hidden;
+    if (kbt > 0) {
+        const TW* band = table + ((size_t)(tok >> 7) * kbt * 128 + (tok & 127)) * 64;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+            o[i] = to_f32(band[(size_t)(i >> 6) * (128 * 64) + (i & 63)]) * scale + to_f32(prow[i]);
+    } else {
+        const TW* row = table + (size_t)tok * hidden;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]) * scale + to_f32(prow[i]);
+    }
+}
+
+extern "C" int hb_embed_pair(const int* tokens, const void* table, int table_dtype, const void* pairs, float* out, int n_tokens,
+                             int hidden, int vocab, int packed, float scale, int buckets, long long mul_prev, long long mul_cur,
+                             const int* positions, const int* tok_seq, const int* seq_start, const int* state_slots, int* state,
+                             long long state_stride, int* status, void* stream) {
+    if (n_tokens == 0) return 0;
+    HB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0 && buckets > 0 && mul_prev >= 0 && mul_cur >= 0 && state_stride >= 1, "embed_pair: bad sizes");
+    HB_REQUIRE((double)vocab * ((double)mul_prev + (double)mul_cur) < 9e18, "embed_pair: the hash would overflow 64 bits");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int kbt = packed ? (hidden + 63) / 64 : 0;
+    if (table_dtype == HB_BF16)
+        hb_launch(embed_pair_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, tokens, (const bf16*)table, (const bf16*)pairs, out, hidden, vocab,
+                  kbt, scale, buckets, mul_prev, mul_cur, positions, tok_seq, seq_start, state_slots, state, state_stride, status);
+    else if (table_dtype == HB_F32)
+        hb_launch(embed_pair_kernel<float>, dim3(n_tokens), dim3(256), 0, s, tokens, (const float*)table, (const float*)pairs, out, hidden,
+                  vocab, kbt, scale, buckets, mul_prev, mul_cur, positions, tok_seq, seq_start, state_slots, state, state_stride, status);
+    else
+        return hb_fail("embed_pair: unsupported table dtype %d", table_dtype);
+    return hb_check_launch("embed_pair");
+}
+
 // -------------------------------------------------------------------------------- rmsnorm
 // out = x * (1 / sqrt(mean(x^2) + eps)) * (offset + w), sum of squares in float32
 // (cpu_backend.c:57-62; cuda_backend.cu:73-85).  Row r of `out` is made from row rows[r]

@@ -15,6 +15,13 @@
 // The order of the entries inside an expert's range depends on the atomics of the plan; an entry's
 // numbers do not, since every output element is one sequential sum over K.
 //
+// moe_route_scores: another router.  Scores s = softmax(z) over ALL router outputs; choice scores c = s + correction; the
+//             outputs form `groups` equal runs of neighbours, a run's score is its largest c, and only outputs of the `keep`
+//             best runs can be chosen; the `top` largest c among those are the token's experts, their weights s (without
+//             the correction) divided by their sum (+ norm_eps).  Router outputs from `n_real` on are identity experts: they
+//             have no matrices, the plan leaves them out, and moe_combine adds weight * h for them.
+// Experts without a gate (moe_glu with w_up null): act = gelu(W_up h), the exact (erf) form.
+//
 // The products are tiled FP32-pipe kernels (MOE_BM rows x MOE_BN columns x MOE_BK): they serve
 // both precisions, with 32-bit accumulation.  glu_clamp is the same activation for a dense
 // [gate | up] matrix (a shared expert, whose products are ordinary matrix products).
@@ -102,6 +109,122 @@ extern "C" int hb_moe_route(const void* h, int h_dtype, long long ldh, const flo
     return hb_check_launch("moe_route");
 }
 
+template <typename TH>
+__global__ void __launch_bounds__(256)
+moe_route_scores_kernel(const TH* __restrict__ h, long long ldh, const float* __restrict__ wr, const float* __restrict__ correction,
+                        int* __restrict__ experts, float* __restrict__ weights, int W, int E, int top, int groups, int keep,
+                        float norm_eps) {
+    pdl_trigger();
+    pdl_wait();
+    h = pdl_fresh(h);
+    extern __shared__ float mr_smem[];
+    float* hs = mr_smem;             // [W]
+    float* ss = hs + W;              // [E]: scores
+    float* cs = ss + E;              // [E]: choice scores, minus infinity once taken or shut out
+    float* gs = cs + E;              // [groups]: a run's score, minus infinity once kept
+    float* kept = gs + groups;       // [groups]: 1 for the runs whose outputs can be chosen
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < W; i += 256) hs[i] = to_f32(h[(size_t)t * ldh + i]);
+    __syncthreads();
+    for (int e = warp; e < E; e += 8) {
+        const float* w = wr + (size_t)e * W;
+        float s = 0.0f;
+        for (int i = lane; i < W; i += 32) s = fmaf(w[i], hs[i], s);
+        s = warp_sum(s);
+        if (lane == 0) ss[e] = s;
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    // softmax over all outputs
+    float zmax = -INFINITY;
+    for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, ss[e]);
+    zmax = warp_max(zmax);
+    float den = 0.0f;
+    for (int e = lane; e < E; e += 32) {
+        const float p = expf(ss[e] - zmax);
+        ss[e] = p;
+        den += p;
+    }
+    den = warp_sum(den);
+    for (int e = lane; e < E; e += 32) {
+        ss[e] = ss[e] / den;
+        cs[e] = ss[e] + (correction ? correction[e] : 0.0f);
+    }
+    __syncwarp();
+    auto arg_best = [&](const float* v, int n, float& best, int& best_i) {       // the largest, lowest index on ties
+        best = -INFINITY;
+        best_i = 0x7fffffff;
+        for (int e = lane; e < n; e += 32)
+            if (v[e] > best || (v[e] == best && e < best_i)) { best = v[e]; best_i = e; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ob > best || (ob == best && oi < best_i)) { best = ob; best_i = oi; }
+        }
+    };
+    if (groups > 1 && keep < groups) {
+        const int per = E / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float b = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; e++) b = fmaxf(b, cs[e]);
+            gs[g] = b;
+            kept[g] = 0.0f;
+        }
+        __syncwarp();
+        for (int k = 0; k < keep; k++) {
+            float b;
+            int bi;
+            arg_best(gs, groups, b, bi);
+            if (bi >= groups) bi = 0;
+            if (lane == 0) { gs[bi] = -INFINITY; kept[bi] = 1.0f; }      // a kept run cannot win again
+            __syncwarp();
+        }
+        // the other runs' outputs are shut out: minus infinity, not zero (choice scores can be negative)
+        for (int e = lane; e < E; e += 32)
+            if (kept[e / per] == 0.0f) cs[e] = -INFINITY;
+        __syncwarp();
+    }
+    float sum = 0.0f;
+    for (int k = 0; k < top; k++) {
+        float b;
+        int bi;
+        arg_best(cs, E, b, bi);
+        if (bi >= E) bi = 0;                              // nothing left (or scores that are not numbers): any output
+        const float p = ss[bi];
+        sum += p;
+        if (lane == 0) {
+            experts[(size_t)t * top + k] = bi;
+            weights[(size_t)t * top + k] = p;
+            cs[bi] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane == 0)
+        for (int k = 0; k < top; k++) weights[(size_t)t * top + k] /= (sum + norm_eps);
+}
+
+extern "C" int hb_moe_route_scores(const void* h, int h_dtype, long long ldh, const float* w_router, const float* correction, int* experts,
+                                   float* weights, int n_tokens, int width, int n_outputs, int top, int groups, int keep, float norm_eps,
+                                   void* stream) {
+    if (n_tokens == 0) return 0;
+    HB_REQUIRE(n_tokens > 0 && width > 0 && n_outputs > 0 && top >= 1 && top <= n_outputs, "moe_route_scores: bad sizes");
+    HB_REQUIRE(groups >= 1 && n_outputs % groups == 0 && keep >= 1 && keep <= groups,
+               "moe_route_scores: %d outputs in %d groups of which %d are kept", n_outputs, groups, keep);
+    HB_REQUIRE(top <= (n_outputs / groups) * keep, "moe_route_scores: the kept groups hold fewer than %d outputs", top);
+    const size_t smem = sizeof(float) * ((size_t)width + 2 * n_outputs + 2 * groups);
+    HB_REQUIRE(smem <= 48 * 1024, "moe_route_scores: width + outputs = %d is too wide", width + n_outputs);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (h_dtype == HB_BF16)
+        hb_launch(moe_route_scores_kernel<bf16>, dim3(n_tokens), dim3(256), smem, s, (const bf16*)h, ldh, w_router, correction, experts, weights,
+                  width, n_outputs, top, groups, keep, norm_eps);
+    else if (h_dtype == HB_F32)
+        hb_launch(moe_route_scores_kernel<float>, dim3(n_tokens), dim3(256), smem, s, (const float*)h, ldh, w_router, correction, experts,
+                  weights, width, n_outputs, top, groups, keep, norm_eps);
+    else return hb_fail("moe_route_scores: unsupported dtype %d", h_dtype);
+    return hb_check_launch("moe_route_scores");
+}
+
 // ------------------------------------------------------------------------------------------------ plan
 // offsets [E + 1], order [entries], tiles [1 + 2 * max_tiles]: tiles[0] = number of tiles, then (expert, first row) pairs
 __global__ void __launch_bounds__(1024)
@@ -116,7 +239,9 @@ moe_plan_kernel(const int* __restrict__ experts, int n_entries, int E, int tile_
     const int tid = threadIdx.x;
     for (int e = tid; e < E; e += 1024) count[e] = 0;
     __syncthreads();
-    for (int i = tid; i < n_entries; i += 1024) atomicAdd(&count[experts[i]], 1);
+    // (an entry whose expert number is E or more belongs to an identity expert: no product walks it)
+    for (int i = tid; i < n_entries; i += 1024)
+        if (experts[i] < E) atomicAdd(&count[experts[i]], 1);
     __syncthreads();
     if (tid == 0) {
         int at = 0, nt = 0;
@@ -134,7 +259,8 @@ moe_plan_kernel(const int* __restrict__ experts, int n_entries, int E, int tile_
         tiles[0] = nt;
     }
     __syncthreads();
-    for (int i = tid; i < n_entries; i += 1024) order[atomicAdd(&cursor[experts[i]], 1)] = i;
+    for (int i = tid; i < n_entries; i += 1024)
+        if (experts[i] < E) order[atomicAdd(&cursor[experts[i]], 1)] = i;
 }
 
 extern "C" int hb_moe_tile_rows(int tensor_cores) { return tensor_cores ? MM_BM : MOE_BM; }
@@ -151,6 +277,14 @@ extern "C" int hb_moe_plan(const int* experts, int n_entries, int n_experts, int
 extern "C" int hb_moe_max_tiles(int n_entries, int n_experts, int tile_rows) { return (n_entries + tile_rows - 1) / tile_rows + n_experts; }
 
 // ------------------------------------------------------------------------------------------------ the experts' products
+__device__ __forceinline__ float moe_gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f)); }
+// the first product's epilogue: the clamped gated unit of two matrices (MODE 1), or the exact gelu of one (MODE 2)
+template <int MODE>
+__device__ __forceinline__ float moe_first_act(float a0, float a1, float limit, float alpha);
+__device__ __forceinline__ float moe_glu(float g, float u, float limit, float alpha);
+template <> __device__ __forceinline__ float moe_first_act<1>(float a0, float a1, float limit, float alpha) { return moe_glu(a0, a1, limit, alpha); }
+template <> __device__ __forceinline__ float moe_first_act<2>(float a0, float a1, float limit, float alpha) { return moe_gelu_erf(a0); }
+template <> __device__ __forceinline__ float moe_first_act<0>(float a0, float a1, float limit, float alpha) { return a0; }
 __device__ __forceinline__ float moe_glu(float g, float u, float limit, float alpha) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
@@ -159,12 +293,13 @@ __device__ __forceinline__ float moe_glu(float g, float u, float limit, float al
 
 // GLU: a rows are h[token of the entry], two weight matrices [E][N][K], result act[slot][N] in TO.
 // else: a rows are act[slot], one weight matrix, result down[entry][N] in 32-bit.
-template <typename TA, typename TW, typename TO, bool GLU>
+template <typename TA, typename TW, typename TO, int MODE>
 __global__ void __launch_bounds__(MOE_THREADS)
 moe_product_kernel(const TA* __restrict__ a, long long lda, const TW* __restrict__ w0, const TW* __restrict__ w1,
                    const int* __restrict__ offsets, const int* __restrict__ order, const int* __restrict__ tiles, int top,
                    TO* __restrict__ out, long long ldo, int N, int K, float limit, float alpha) {
     pdl_trigger();
+    constexpr bool GLU = MODE == 1, FIRST = MODE != 0;        // FIRST: rows gathered by token, results at the slot
     __shared__ float As[MOE_BK][MOE_BM + 1];
     __shared__ float B0[MOE_BK][MOE_BN + 1];
     __shared__ float B1[GLU ? MOE_BK : 1][MOE_BN + 1];
@@ -181,8 +316,8 @@ moe_product_kernel(const TA* __restrict__ a, long long lda, const TW* __restrict
     const int tid = threadIdx.x;
     if (tid < MOE_BM) {
         const int entry = tid < rows ? order[r0 + tid] : -1;
-        row_src[tid] = entry < 0 ? -1 : (GLU ? entry / top : r0 + tid);
-        row_dst[tid] = entry < 0 ? -1 : (GLU ? r0 + tid : entry);
+        row_src[tid] = entry < 0 ? -1 : (FIRST ? entry / top : r0 + tid);
+        row_dst[tid] = entry < 0 ? -1 : (FIRST ? r0 + tid : entry);
     }
     __syncthreads();
     const TW* we0 = w0 + (size_t)e * N * K;
@@ -229,7 +364,7 @@ moe_product_kernel(const TA* __restrict__ a, long long lda, const TW* __restrict
         for (int j = 0; j < 2; j++) {
             const int n = n0 + tx * 2 + j;
             if (n >= N) continue;
-            const float v = GLU ? moe_glu(acc0[i][j], acc1[i][j], limit, alpha) : acc0[i][j];
+            const float v = moe_first_act<MODE>(acc0[i][j], acc1[i][j], limit, alpha);
             out[(size_t)dst * ldo + n] = from_f32<TO>(v);
         }
     }
@@ -240,13 +375,14 @@ moe_product_kernel(const TA* __restrict__ a, long long lda, const TW* __restrict
 // plan tile of MM_BM rows and MM_BN output columns; rows (gathered by the plan's order) and weight rows arrive through a
 // MM_STAGES-deep cp.async pipeline into XOR-swizzled shared memory and are read with ldmatrix; eight warps as 4 (rows) x 2
 // (columns), each 16 rows x 32 columns (and both matrices for the gated unit, whose activation is the epilogue).
-template <bool GLU, typename TO>
+template <int MODE, typename TO>
 __global__ void __launch_bounds__(MM_THREADS)
 moe_product_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __restrict__ w0, const bf16* __restrict__ w1,
                        const int* __restrict__ offsets, const int* __restrict__ order, const int* __restrict__ tiles, int top,
                        TO* __restrict__ out, long long ldo, int N, int K, float limit, float alpha) {
     pdl_trigger();
     extern __shared__ __align__(128) unsigned char mm_smem[];
+    constexpr bool GLU = MODE == 1, FIRST = MODE != 0;
     constexpr int TILE_BYTES = MM_BM * MM_BK * 2, MATS = GLU ? 3 : 2, STAGE_BYTES = TILE_BYTES * MATS;
     static_assert(MM_BM == MM_BN && MM_BK * 2 == 128, "one tile shape and 128-byte rows for rows and weights");
     __shared__ int row_src[MM_BM], row_dst[MM_BM];
@@ -262,8 +398,8 @@ moe_product_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid < MM_BM) {
         const int entry = tid < rows ? order[r0 + tid] : -1;
-        row_src[tid] = entry < 0 ? -1 : (GLU ? entry / top : r0 + tid);
-        row_dst[tid] = entry < 0 ? -1 : (GLU ? r0 + tid : entry);
+        row_src[tid] = entry < 0 ? -1 : (FIRST ? entry / top : r0 + tid);
+        row_dst[tid] = entry < 0 ? -1 : (FIRST ? r0 + tid : entry);
     }
     __syncthreads();
     const bf16* we0 = w0 + (size_t)e * N * K;
@@ -346,23 +482,23 @@ moe_product_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __
                 const int n = n0 + wn * 32 + nt * 8 + 2 * tg + j;
                 if (n >= N) continue;
                 const float v0 = acc0[nt][2 * hr + j];
-                out[(size_t)dst * ldo + n] = from_f32<TO>(GLU ? moe_glu(v0, acc1[GLU ? nt : 0][2 * hr + j], limit, alpha) : v0);
+                out[(size_t)dst * ldo + n] = from_f32<TO>(moe_first_act<MODE>(v0, acc1[GLU ? nt : 0][2 * hr + j], limit, alpha));
             }
     }
 }
 
-template <bool GLU, typename TO>
+template <int MODE, typename TO>
 static int moe_mma_launch(dim3 grid, cudaStream_t s, const bf16* a, long long lda, const bf16* w0, const bf16* w1, const int* offsets,
                           const int* order, const int* tiles, int top, TO* out, long long ldo, int N, int K, float limit, float alpha) {
-    constexpr int SMEM = MM_STAGES * MM_BM * MM_BK * 2 * (GLU ? 3 : 2);
+    constexpr int SMEM = MM_STAGES * MM_BM * MM_BK * 2 * (MODE == 1 ? 3 : 2);
     static bool done[HB_MAX_DEVICES] = {};
     const int slot = hb_device_slot();
     if (!done[slot]) {
-        cudaError_t e = cudaFuncSetAttribute(moe_product_mma_kernel<GLU, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(moe_product_mma_kernel<MODE, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return hb_fail("moe: shared memory: %s", cudaGetErrorString(e));
         done[slot] = true;
     }
-    hb_launch(moe_product_mma_kernel<GLU, TO>, dim3(grid), dim3(MM_THREADS), SMEM, s, a, lda, w0, w1, offsets, order, tiles, top, out, ldo, N, K,
+    hb_launch(moe_product_mma_kernel<MODE, TO>, dim3(grid), dim3(MM_THREADS), SMEM, s, a, lda, w0, w1, offsets, order, tiles, top, out, ldo, N, K,
               limit, alpha);
     return 0;
 }
@@ -376,18 +512,32 @@ extern "C" int hb_moe_glu(const void* h, int h_dtype, long long ldh, const void*
     cudaStream_t s = (cudaStream_t)stream;
     if (tensor_cores) {
         HB_REQUIRE(h_dtype == HB_BF16 && w_dtype == HB_BF16 && act_dtype == HB_BF16 && width % 8 == 0 && ldh % 8 == 0 &&
-                   (((uintptr_t)h | (uintptr_t)w_gate | (uintptr_t)w_up) & 15) == 0,
+                   (((uintptr_t)h | (uintptr_t)w_gate | (uintptr_t)w_up) & 15) == 0,   /* a null w_up: one matrix */
                    "moe_glu: the tensor-core variant needs bfloat16 operands with 16-byte aligned rows");
         grid.y = (ff + MM_BN - 1) / MM_BN;
-        if (moe_mma_launch<true, bf16>(grid, s, (const bf16*)h, ldh, (const bf16*)w_gate, (const bf16*)w_up, offsets, order, tiles, top,
-                                       (bf16*)act, lda, ff, width, limit, alpha)) return 1;
+        if (w_up == nullptr) {
+            if (moe_mma_launch<2, bf16>(grid, s, (const bf16*)h, ldh, (const bf16*)w_gate, (const bf16*)nullptr, offsets, order, tiles, top,
+                                        (bf16*)act, lda, ff, width, limit, alpha)) return 1;
+        } else if (moe_mma_launch<1, bf16>(grid, s, (const bf16*)h, ldh, (const bf16*)w_gate, (const bf16*)w_up, offsets, order, tiles, top,
+                                           (bf16*)act, lda, ff, width, limit, alpha)) return 1;
+        return hb_check_launch("moe_glu");
+    }
+    if (w_up == nullptr) {
+        // one matrix per expert (passed as w_gate) and the exact gelu
+        if (h_dtype == HB_BF16 && w_dtype == HB_BF16 && act_dtype == HB_BF16)
+            hb_launch(moe_product_kernel<bf16, bf16, bf16, 2>, dim3(grid), dim3(MOE_THREADS), 0, s, (const bf16*)h, ldh, (const bf16*)w_gate,
+                      (const bf16*)nullptr, offsets, order, tiles, top, (bf16*)act, lda, ff, width, limit, alpha);
+        else if (h_dtype == HB_F32 && w_dtype == HB_F32 && act_dtype == HB_F32)
+            hb_launch(moe_product_kernel<float, float, float, 2>, dim3(grid), dim3(MOE_THREADS), 0, s, (const float*)h, ldh, (const float*)w_gate,
+                      (const float*)nullptr, offsets, order, tiles, top, (float*)act, lda, ff, width, limit, alpha);
+        else return hb_fail("moe_glu: unsupported dtypes h %d w %d act %d", h_dtype, w_dtype, act_dtype);
         return hb_check_launch("moe_glu");
     }
     if (h_dtype == HB_BF16 && w_dtype == HB_BF16 && act_dtype == HB_BF16)
-        hb_launch(moe_product_kernel<bf16, bf16, bf16, true>, dim3(grid), dim3(MOE_THREADS), 0, s, (const bf16*)h, ldh, (const bf16*)w_gate,
+        hb_launch(moe_product_kernel<bf16, bf16, bf16, 1>, dim3(grid), dim3(MOE_THREADS), 0, s, (const bf16*)h, ldh, (const bf16*)w_gate,
                   (const bf16*)w_up, offsets, order, tiles, top, (bf16*)act, lda, ff, width, limit, alpha);
     else if (h_dtype == HB_F32 && w_dtype == HB_F32 && act_dtype == HB_F32)
-        hb_launch(moe_product_kernel<float, float, float, true>, dim3(grid), dim3(MOE_THREADS), 0, s, (const float*)h, ldh, (const float*)w_gate,
+        hb_launch(moe_product_kernel<float, float, float, 1>, dim3(grid), dim3(MOE_THREADS), 0, s, (const float*)h, ldh, (const float*)w_gate,
                   (const float*)w_up, offsets, order, tiles, top, (float*)act, lda, ff, width, limit, alpha);
     else return hb_fail("moe_glu: unsupported dtypes h %d w %d act %d", h_dtype, w_dtype, act_dtype);
     return hb_check_launch("moe_glu");
@@ -404,42 +554,95 @@ extern "C" int hb_moe_down(const void* act, int act_dtype, long long lda, const 
         HB_REQUIRE(act_dtype == HB_BF16 && w_dtype == HB_BF16 && ff % 8 == 0 && lda % 8 == 0 && (((uintptr_t)act | (uintptr_t)w_down) & 15) == 0,
                    "moe_down: the tensor-core variant needs bfloat16 operands with 16-byte aligned rows");
         grid.y = (width + MM_BN - 1) / MM_BN;
-        if (moe_mma_launch<false, float>(grid, s, (const bf16*)act, lda, (const bf16*)w_down, (const bf16*)nullptr, offsets, order, tiles, top,
+        if (moe_mma_launch<0, float>(grid, s, (const bf16*)act, lda, (const bf16*)w_down, (const bf16*)nullptr, offsets, order, tiles, top,
                                          down, ldd, width, ff, 0.0f, 0.0f)) return 1;
         return hb_check_launch("moe_down");
     }
     if (act_dtype == HB_BF16 && w_dtype == HB_BF16)
-        hb_launch(moe_product_kernel<bf16, bf16, float, false>, dim3(grid), dim3(MOE_THREADS), 0, s, (const bf16*)act, lda, (const bf16*)w_down,
+        hb_launch(moe_product_kernel<bf16, bf16, float, 0>, dim3(grid), dim3(MOE_THREADS), 0, s, (const bf16*)act, lda, (const bf16*)w_down,
                   (const bf16*)nullptr, offsets, order, tiles, top, down, ldd, width, ff, 0.0f, 0.0f);
     else if (act_dtype == HB_F32 && w_dtype == HB_F32)
-        hb_launch(moe_product_kernel<float, float, float, false>, dim3(grid), dim3(MOE_THREADS), 0, s, (const float*)act, lda, (const float*)w_down,
+        hb_launch(moe_product_kernel<float, float, float, 0>, dim3(grid), dim3(MOE_THREADS), 0, s, (const float*)act, lda, (const float*)w_down,
                   (const float*)nullptr, offsets, order, tiles, top, down, ldd, width, ff, 0.0f, 0.0f);
     else return hb_fail("moe_down: unsupported dtypes act %d w %d", act_dtype, w_dtype);
     return hb_check_launch("moe_down");
 }
 
 // ------------------------------------------------------------------------------------------------ combine
+// `experts` with `n_real`: an entry whose expert number is n_real or more is an identity expert, whose result is the
+// token's input row of `h` itself
+template <typename TH>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ down, long long ldd, const float* __restrict__ weights, int top, float* __restrict__ out,
-                   long long ldo, int width, int accumulate) {
+                   long long ldo, int width, int accumulate, const int* __restrict__ experts, int n_real, const TH* __restrict__ h,
+                   long long ldh) {
     pdl_trigger();
     pdl_wait();
     down = pdl_fresh(down);
     weights = pdl_fresh(weights);
+    experts = pdl_fresh(experts);
+    h = pdl_fresh(h);
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < width; c += 256) {
         float v = accumulate ? out[(size_t)t * ldo + c] : 0.0f;
-        for (int k = 0; k < top; k++) v = fmaf(weights[(size_t)t * top + k], down[((size_t)t * top + k) * ldd + c], v);
+        for (int k = 0; k < top; k++) {
+            const bool same = experts != nullptr && experts[(size_t)t * top + k] >= n_real;
+            v = fmaf(weights[(size_t)t * top + k], same ? to_f32(h[(size_t)t * ldh + c]) : down[((size_t)t * top + k) * ldd + c], v);
+        }
         out[(size_t)t * ldo + c] = v;
     }
 }
 
 extern "C" int hb_moe_combine(const float* down, long long ldd, const float* weights, int top, float* out, long long ldo, int n_tokens,
-                              int width, int accumulate, void* stream) {
+                              int width, int accumulate, const int* experts, int n_real, const void* h, int h_dtype, long long ldh,
+                              void* stream) {
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && width > 0 && top >= 1, "moe_combine: bad sizes");
-    hb_launch(moe_combine_kernel, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, down, ldd, weights, top, out, ldo, width, accumulate);
+    HB_REQUIRE(experts == nullptr || (h != nullptr && ldh >= width && n_real >= 0), "moe_combine: identity experts need the input rows");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (experts != nullptr && h_dtype == HB_BF16)
+        hb_launch(moe_combine_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, down, ldd, weights, top, out, ldo, width, accumulate, experts, n_real,
+                  (const bf16*)h, ldh);
+    else if (experts == nullptr || h_dtype == HB_F32)
+        hb_launch(moe_combine_kernel<float>, dim3(n_tokens), dim3(256), 0, s, down, ldd, weights, top, out, ldo, width, accumulate, experts, n_real,
+                  (const float*)h, ldh);
+    else return hb_fail("moe_combine: unsupported input dtype %d", h_dtype);
     return hb_check_launch("moe_combine");
+}
+
+// ------------------------------------------------------------------------------------------------ gelu_unit
+// kind 0: out = gelu_tanh(in[:, :F]) * in[:, F:2F]  (a gated unit with the tanh form of gelu)
+// kind 1: out = gelu_erf(in[:, :F]) * (row_gate >= 0 ? sigmoid(in[:, row_gate]) : 1)  (one matrix, the exact gelu, and a
+//         per-row gate from one more column of the same product)
+template <typename TO>
+__global__ void __launch_bounds__(256)
+gelu_unit_kernel(const float* __restrict__ in, long long ldi, TO* __restrict__ out, long long ldo, int F, int kind, int row_gate) {
+    pdl_trigger();
+    pdl_wait();
+    in = pdl_fresh(in);
+    const float* r = in + (size_t)blockIdx.y * ldi;
+    float gate = 1.0f;
+    if (kind == 1 && row_gate >= 0) gate = 1.0f / (1.0f + expf(-r[row_gate]));
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < F; i += gridDim.x * 256) {
+        const float zv = r[i];
+        float v;
+        if (kind == 0) v = 0.5f * zv * (1.0f + tanhf(0.7978845608028654f * (zv + 0.044715f * zv * zv * zv))) * r[F + i];
+        else v = moe_gelu_erf(zv) * gate;
+        out[(size_t)blockIdx.y * ldo + i] = from_f32<TO>(v);
+    }
+}
+
+extern "C" int hb_gelu_unit(const float* in, long long ldi, void* out, int out_dtype, long long ldo, int n_rows, int F, int kind,
+                            int row_gate, void* stream) {
+    if (n_rows == 0) return 0;
+    HB_REQUIRE(n_rows > 0 && n_rows <= 65535 && F > 0 && ldo >= F && (kind == 0 || kind == 1), "gelu_unit: bad sizes");
+    HB_REQUIRE(ldi >= (kind == 0 ? 2 * F : F) && row_gate < ldi, "gelu_unit: input rows are too short");
+    dim3 grid(min((F + 255) / 256, 64), n_rows);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == HB_BF16) hb_launch(gelu_unit_kernel<bf16>, dim3(grid), dim3(256), 0, s, in, ldi, (bf16*)out, ldo, F, kind, row_gate);
+    else if (out_dtype == HB_F32) hb_launch(gelu_unit_kernel<float>, dim3(grid), dim3(256), 0, s, in, ldi, (float*)out, ldo, F, kind, row_gate);
+    else return hb_fail("gelu_unit: unsupported output dtype %d", out_dtype);
+    return hb_check_launch("gelu_unit");
 }
 
 // ------------------------------------------------------------------------------------------------ glu_clamp

@@ -89,8 +89,12 @@ class DecoderModel:
                 out[i] = need
         return out
 
+    EMBEDDING_STATE = -1        # the key of the embedding's per-sequence state beside the plan entries'
+
     def state_needs(self) -> Dict[int, StateNeed]:
         out = {}
+        if getattr(self.embedding, "state_need", None) is not None and self.embedding.state_need() is not None:
+            out[self.EMBEDDING_STATE] = self.embedding.state_need()
         for i, e in enumerate(self.spec.plan):
             need = self.blocks[e.layer].state_need()
             if need is not None:
@@ -126,7 +130,10 @@ class DecoderModel:
         ws, cap, T = self.ctx.workspace, self.ctx.max_step_tokens, step.num_tokens
         H, V = self.spec.hidden_size, self.spec.vocab_size
         x = ws.buffer("model.x", (cap, H), torch.float32)[:T]
-        self.embedding.forward(step.tokens, x)
+        if getattr(self.embedding, "state_need", None) is not None:
+            self.embedding.forward(step.tokens, x, step=step, state=cache.state_view(self.EMBEDDING_STATE))
+        else:
+            self.embedding.forward(step.tokens, x)
         # Norms at the seam between two blocks may be folded into the products around them: a block
         # that can says what it needs (fold_request), the block in front prepares it and hands on
         # what it prepared.

@@ -35,15 +35,15 @@ _SIGNATURES = {
     "hb_relu2": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
     "hb_qkv_prepare": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr,
                        _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
-                       _c_ptr, _c_int, _c_ptr, _c_ptr],
+                       _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_attention_sink": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
-                          _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+                          _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_head_mix": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ll, _c_ptr],
     "hb_attention_heads": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
-                           _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
-                           _c_ptr],
+                           _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int,
+                           _c_int, _c_ptr, _c_ptr],
     "hb_attention_sink_prefill": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
-                                  _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+                                  _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr],
     "hb_head_mix_splits": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ll, _c_ptr],
     "hb_mlstm_scan": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                       _c_int, _c_int, _c_ptr],
@@ -112,7 +112,17 @@ _SIGNATURES = {
                    _c_int, _c_float, _c_float, _c_int, _c_ptr],
     "hb_moe_down": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_int,
                     _c_ptr],
-    "hb_moe_combine": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_moe_combine": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ll, _c_ptr],
+    "hb_moe_route_scores": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                            _c_ptr],
+    "hb_gelu_unit": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_embed_pair": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ll, _c_ll, _c_ptr, _c_ptr,
+                      _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr],
+    "hb_scaled_add_norm": [_c_ptr, _c_ll, _c_float, _c_ptr, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
+    "hb_normed_sum": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_float, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_head_scan": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_float,
+                     _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                     _c_ptr, _c_ll, _c_ptr],
     "hb_glu_clamp": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_float, _c_float, _c_ptr],
 }
 
@@ -386,6 +396,24 @@ class Ops:
                    table.shape[0], 1 if packed else 0, float(scale), self.status.data_ptr(), self._stream())
         self.launches += 1
 
+    def embed_pair(self, step, table, pairs, state, out, buckets: int, mul_prev: int, mul_cur: int, scale: float = 1.0) -> None:
+        """``out[t] = table[token] * scale + pairs[row]`` in 32-bit with ``row = (previous * mul_prev + token * mul_cur) mod
+        buckets``, and ``row = buckets`` (the last row of ``pairs``) for a sequence's first token.  ``state`` int32 ``[slots, 1]``:
+        every sequence's last token, read by the step's first token and brought up to date."""
+        packed = isinstance(table, PackedWeight)
+        self._dev(step.tokens, table.data if packed else table, pairs, state, out)
+        T, H = out.shape
+        if out.dtype != torch.float32 or not out.is_contiguous() or not (packed or table.is_contiguous()) or not pairs.is_contiguous() \
+                or table.shape[1] != H or tuple(pairs.shape) != (buckets + 1, H) or pairs.dtype != table.dtype or step.tokens.numel() != T:
+            raise KernelError("embed_pair: contiguous tables of one dtype ([vocab, width], [buckets + 1, width]) and a float32 output expected")
+        if state.dtype != torch.int32 or state.dim() != 2 or state.stride(1) != 1:
+            raise KernelError("embed_pair: state must be int32 [slots, 1]")
+        self._call("hb_embed_pair", step.tokens.data_ptr(), table.data_ptr(), _code(table), pairs.data_ptr(), out.data_ptr(), T, H,
+                   table.shape[0], 1 if packed else 0, float(scale), int(buckets), int(mul_prev), int(mul_cur), step.positions.data_ptr(),
+                   step.tok_seq.data_ptr(), step.seq_start.data_ptr(), step.state_slots.data_ptr(), state.data_ptr(), state.stride(0),
+                   self.status.data_ptr(), self._stream())
+        self.launches += 1
+
     def rmsnorm(self, x, weight, eps: float, offset: float, out, rows=None) -> None:
         self._dev(x, weight, out, rows)
         if x.dtype != torch.float32 or weight.dtype != torch.float32 or not x.is_contiguous() \
@@ -506,19 +534,21 @@ class Ops:
     # ------------------------------------------------------------------ attention with kept first tokens and mixed heads
     def qkv_prepare(self, proj, bias, table, rot: int, heads: int, kv_heads: int, head_dim: int, v_dim: int, unit_norm: bool,
                     eps: float, q_out, cache, step, append: bool, v_lambda=None, v_first=None, v_mode: int = 0,
-                    norm_weights=None) -> None:
+                    norm_weights=None, interleaved: bool = False, v_from_k: bool = False) -> None:
         """From a step's projections ``[q | k | v]``: biases added, queries and keys turned by ``table`` and (``unit_norm``)
         divided by their root mean square per head; queries to ``q_out``, keys and values into the cache.  ``norm_weights``
         ``(wq, wk)`` (float32 ``[head_dim]`` each): instead, every head of q and of k is divided by its root mean square and
         multiplied by its weight BEFORE the rotation.  ``v_mode`` 1 also
         keeps the values in ``v_first`` (float32 ``[tokens, kv_heads * v_dim]``), 2 mixes them with it:
-        ``v <- (1 - v_lambda) v + v_lambda v_first``."""
+        ``v <- (1 - v_lambda) v + v_lambda v_first``.  ``interleaved``: the rotation turns the pairs ``(2i, 2i + 1)`` instead of
+        ``(i, i + rot/2)``.  ``v_from_k``: there is no value projection; the values are the keys as projected (with their bias,
+        before norm and rotation), and the projections' row is ``[q | k]``."""
         self._dev(proj, bias, table, q_out, cache.k, cache.v, v_lambda, v_first)
         T = proj.shape[0]
         if norm_weights is not None and unit_norm:
             raise KernelError("qkv_prepare: one norm of queries and keys at a time")
-        width = heads * head_dim + kv_heads * (head_dim + v_dim)
-        if proj.shape[1] < width or tuple(q_out.shape) != (T, heads * head_dim):
+        width = heads * head_dim + kv_heads * (head_dim + (0 if v_from_k else v_dim))
+        if proj.shape[1] < width or tuple(q_out.shape) != (T, heads * head_dim) or (v_from_k and (v_dim != head_dim or v_mode)):
             raise KernelError("qkv_prepare: shapes do not agree")
         if rot and (table is None or table.shape[0] != T or table.shape[1] != rot // 2):
             raise KernelError("qkv_prepare: rotary table does not match the tokens")
@@ -537,13 +567,15 @@ class Ops:
                    q_out.data_ptr(), _code(q_out), _rows(q_out, "queries"), cache.k.data_ptr(), cache.v.data_ptr(), _code(cache.k),
                    pt.data_ptr(), pt.shape[1], step.tok_seq.data_ptr(), step.positions.data_ptr(), T, cache.k.shape[0],
                    1 if append else 0, self._f32_vec(v_lambda, 1, "value mix") if v_lambda is not None else None,
-                   v_first.data_ptr() if v_first is not None else None, int(v_mode), self.status.data_ptr(), self._stream())
+                   v_first.data_ptr() if v_first is not None else None, int(v_mode), 1 if interleaved else 0, 1 if v_from_k else 0,
+                   self.status.data_ptr(), self._stream())
         self.launches += 1
 
     def attention_sink(self, q, heads: int, kv_heads: int, head_dim: int, v_dim: int, cache, step, partial, scale: float,
-                       window: Optional[int], keep_first: int, all_values: bool) -> None:
+                       window: Optional[int], keep_first: int, all_values: bool, chunk: int = 0, sink=None) -> None:
         """Causal attention where a query at position p sees key s if ``p - s < window`` or ``s < keep_first``
-        (``window`` None: every earlier key).  ``partial`` float32 ``[tokens, heads, kv_heads if all_values else 1,
+        (``window`` None: every earlier key); with ``chunk`` instead, if s lies in p's own run of ``chunk`` positions (runs
+        counted from the sequence's start).  ``sink`` float32 ``[heads]``: the softmax's sum holds ``exp(sink[h])`` once more.  ``partial`` float32 ``[tokens, heads, kv_heads if all_values else 1,
         v_dim]``: each head's softmax weights applied to the values of every key/value head, or of its own."""
         self._dev(q, cache.k, cache.v, partial)
         T = q.shape[0]
@@ -555,8 +587,9 @@ class Ops:
         pt = step.page_tables[cache.group]
         self._call("hb_attention_sink", q.data_ptr(), _code(q), _rows(q, "queries"), cache.k.data_ptr(), cache.v.data_ptr(),
                    _code(cache.k), pt.data_ptr(), pt.shape[1], step.tok_seq.data_ptr(), step.positions.data_ptr(),
-                   partial.data_ptr(), T, heads, kv_heads, head_dim, v_dim, float(scale), int(window) if window else 0,
-                   int(keep_first), 1 if all_values else 0, cache.k.shape[0], self.status.data_ptr(), self._stream())
+                   partial.data_ptr(), T, heads, kv_heads, head_dim, v_dim, float(scale), int(window) if window and not chunk else 0,
+                   int(keep_first), int(chunk), self._f32_vec(sink, heads, "sink") if sink is not None else None,
+                   1 if all_values else 0, cache.k.shape[0], self.status.data_ptr(), self._stream())
         self.launches += 1
 
     def _head_gate(self, gate, T: int, heads: int):
@@ -591,7 +624,7 @@ class Ops:
                     and sum((n + 63) // 64 for n in step.host_new) <= 65535)
 
     def attention_sink_prefill(self, q, heads: int, kv_heads: int, head_dim: int, v_dim: int, cache, step, partial, scale: float,
-                               window: Optional[int], keep_first: int, all_values: bool) -> None:
+                               window: Optional[int], keep_first: int, all_values: bool, chunk: int = 0, sink=None) -> None:
         """``attention_sink`` on the tensor cores, 64 query tokens of a sequence per block: ``partial`` float32
         ``[tokens, heads, kv_heads if all_values else 1, v_dim]``, normalised."""
         self._dev(q, cache.k, cache.v, partial)
@@ -606,7 +639,8 @@ class Ops:
         q_blocks = sum((n + 63) // 64 for n in step.host_new)
         self._call("hb_attention_sink_prefill", q.data_ptr(), _rows(q, "queries"), cache.k.data_ptr(), cache.v.data_ptr(), pt.data_ptr(),
                    pt.shape[1], step.seq_start.data_ptr(), step.seq_pos0.data_ptr(), partial.data_ptr(), step.num_seqs, q_blocks,
-                   heads, kv_heads, head_dim, v_dim, n_val, float(scale), int(window) if window else 0, int(keep_first),
+                   heads, kv_heads, head_dim, v_dim, n_val, float(scale), int(window) if window and not chunk else 0, int(keep_first),
+                   int(chunk), self._f32_vec(sink, heads, "sink") if sink is not None else None,
                    cache.k.shape[0], self.status.data_ptr(), self._stream())
         self.launches += 1
 
@@ -636,7 +670,8 @@ class Ops:
         return splits, (splits == 1 and whole)
 
     def attention_heads(self, q, heads: int, kv_heads: int, head_dim: int, v_dim: int, cache, step, scale: float, window: Optional[int],
-                        keep_first: int, splits: int, mix=None, out=None, ones: int = 0, partial=None, ml=None) -> None:
+                        keep_first: int, splits: int, mix=None, out=None, ones: int = 0, partial=None, ml=None, chunk: int = 0,
+                        sink=None) -> None:
         """The attention of ``attention_sink`` with one block per (token, key split) for all heads (each head's weights on
         the values of every key/value head).  With ``out`` (one split): the normalised, head-mixed output and ``ones``
         more columns (a one, then zeros).  Else ``partial`` float32 ``[tokens, heads, splits, kv_heads * v_dim]``
@@ -656,7 +691,8 @@ class Ops:
                    partial.data_ptr() if partial is not None else None, ml.data_ptr() if ml is not None else None,
                    self._f32_vec(mix, heads * heads, "head mix") if mix is not None else None,
                    out.data_ptr() if out is not None else None, _rows(out, "attention output") if out is not None else 0, ones,
-                   T, heads, kv_heads, head_dim, v_dim, float(scale), int(window) if window else 0, int(keep_first), int(splits),
+                   T, heads, kv_heads, head_dim, v_dim, float(scale), int(window) if window and not chunk else 0, int(keep_first),
+                   int(chunk), self._f32_vec(sink, heads, "sink") if sink is not None else None, int(splits),
                    cache.k.shape[0], 1 if self.use_mma_attention else 0, self.status.data_ptr(), self._stream())
         self.launches += 1
 
@@ -1041,6 +1077,35 @@ class Ops:
         self._call("hb_scaled_sum", a.data_ptr(), float(sa), b.data_ptr(), float(sb), out.data_ptr(), out.numel(), self._stream())
         self.launches += 1
 
+    def scaled_add_norm(self, y, m: float, x, then=None, then_out=None) -> None:
+        """``x += m * y`` row by row in 32-bit; with ``then = (weight, eps, offset)`` and ``then_out`` also ``then_out = x /
+        sqrt(mean(x^2) + eps) * (offset + weight)`` of the new rows, in the same pass."""
+        self._dev(y, x, then_out)
+        T, n = x.shape
+        if y.dtype != torch.float32 or x.dtype != torch.float32 or tuple(y.shape) != (T, n) or (then is None) != (then_out is None):
+            raise KernelError("scaled_add_norm: float32 [tokens, width] input and residual expected")
+        w2 = e2 = o2 = None
+        if then is not None:
+            w2, e2, o2 = then
+            if tuple(then_out.shape) != (T, n):
+                raise KernelError("scaled_add_norm: the norm's output does not match")
+        self._call("hb_scaled_add_norm", y.data_ptr(), _rows(y, "sublayer result"), float(m), x.data_ptr(), _rows(x, "residual"),
+                   self._f32_vec(w2, n, "norm weight") if then is not None else None, float(e2 or 0.0), float(o2 or 0.0),
+                   then_out.data_ptr() if then is not None else None, _code(then_out) if then is not None else 0,
+                   _rows(then_out, "norm output") if then is not None else 0, T, n, self._stream())
+        self.launches += 1
+
+    def normed_sum(self, a, wa, b, wb, eps: float, out, accumulate: bool = False) -> None:
+        """``out (+)= a / sqrt(mean(a^2) + eps) * wa + b / sqrt(mean(b^2) + eps) * wb`` row by row, everything float32."""
+        self._dev(a, wa, b, wb, out)
+        T, n = out.shape
+        if any(t.dtype != torch.float32 or tuple(t.shape) != (T, n) for t in (a, b, out)):
+            raise KernelError("normed_sum: float32 [tokens, width] tensors expected")
+        self._call("hb_normed_sum", a.data_ptr(), _rows(a, "first result"), self._f32_vec(wa, n, "norm weight"), b.data_ptr(),
+                   _rows(b, "second result"), self._f32_vec(wb, n, "norm weight"), float(eps), out.data_ptr(), _rows(out, "sum"), T, n,
+                   1 if accumulate else 0, self._stream())
+        self.launches += 1
+
     # ------------------------------------------------------------------ window + pooled blocks, sigmoid weights
     def qk_norm_append(self, proj, q_weight, k_weight, eps: float, heads: int, kv_heads: int, head_dim: int, v_dim: int, q_out, cache,
                        step, append: bool) -> None:
@@ -1354,7 +1419,81 @@ class Ops:
                    carry.data_ptr() if carry is not None else None, carry.numel() if carry is not None else 0, self._stream())
         self.launches += 3 if chunked else 1
 
+    HEAD_SCAN_CHUNK_FROM = 256      # steps whose longest portion has at least so many tokens may run the memory in chunks
+    HEAD_SCAN_CHUNK = 64
+
+    def head_scan(self, u, k, q, decay_raw, decay_bias, state, step, out, heads: int, groups: int, head_dim: int, n_state: int,
+                  a_log=None, inv_tau: float = 1.0, skip=None, z=None, q_scale: float = 1.0, workspace=None,
+                  chunked: Optional[bool] = None) -> None:
+        """A recurrent memory per head whose decay depends on the token, over a step's tokens, sequence by sequence:
+        ``S <- a S + s u k^T``, ``y = q_scale S^T q + skip u``, ``out = y silu(z)`` (``z`` None: no gate).  ``u`` float32
+        ``[tokens, heads * head_dim]``, ``k`` and ``q`` float32 ``[tokens, groups * n_state]`` (heads share them in ``groups``
+        runs).  With ``a_log`` (float32 ``[heads]``): ``decay_raw [tokens, heads]`` are step sizes before bias and softplus,
+        ``a = exp(-exp(a_log) dt)`` and ``s = dt``.  Without: ``decay_raw [tokens, heads * n_state]``, ``a = sigmoid(decay_raw +
+        decay_bias) ^ inv_tau`` per state index and ``s = 1``.  ``state`` float32 ``[slots, heads * head_dim * n_state]``.
+        ``chunked`` (default: long portions while heads, channels and sequences are too few to fill the device, given a
+        ``workspace``): the tokens of a sequence are cut into chunks that run side by side (three launches)."""
+        self._dev(u, k, q, decay_raw, decay_bias, state, out, a_log, skip, z)
+        T = u.shape[0]
+        mode = 0 if a_log is not None else 1
+        width = heads * head_dim
+        if any(t.dtype != torch.float32 for t in (u, k, q, decay_raw)) or tuple(u.shape) != (T, width) or tuple(out.shape) != (T, width) \
+                or tuple(k.shape) != (T, groups * n_state) or tuple(q.shape) != (T, groups * n_state) \
+                or tuple(decay_raw.shape) != (T, heads * (n_state if mode else 1)) or (z is not None and (z.dtype != torch.float32 or tuple(z.shape) != (T, width))):
+            raise KernelError("head_scan: shapes or dtypes do not agree")
+        if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != width * n_state or state.stride(1) != 1:
+            raise KernelError("head_scan: state must be float32 [slots, heads * head_dim * n_state]")
+        if chunked is None:
+            lanes = 4 if n_state <= 16 else min(32, n_state // 4)
+            chunked = (workspace is not None and not step.is_decode and step.max_new >= self.HEAD_SCAN_CHUNK_FROM
+                       and -(-head_dim // (256 // max(lanes, 4))) * heads * step.num_seqs < self.sm_count)
+        chunk_len, max_chunks, carry = 0, 0, None
+        if chunked:
+            chunk_len = self.HEAD_SCAN_CHUNK
+            max_chunks = -(-step.max_new // chunk_len)
+            carry = workspace.buffer("head_scan.carry", (step.num_seqs * max_chunks * heads * (2 * head_dim * n_state + (n_state if mode else 1)),),
+                                     torch.float32)
+        self._call("hb_head_scan", u.data_ptr(), _rows(u, "memory input"), k.data_ptr(), _rows(k, "memory keys"), q.data_ptr(),
+                   _rows(q, "memory queries"), z.data_ptr() if z is not None else None, _rows(z, "memory gate") if z is not None else 0,
+                   decay_raw.data_ptr(), _rows(decay_raw, "decay input"),
+                   self._f32_vec(decay_bias, heads * (n_state if mode else 1), "decay bias"),
+                   self._f32_vec(a_log, heads, "A_log") if a_log is not None else None, float(inv_tau),
+                   self._f32_vec(skip, heads, "skip weight") if skip is not None else None, float(q_scale), state.data_ptr(),
+                   state.stride(0), step.state_slots.data_ptr(), step.seq_start.data_ptr(), out.data_ptr(), _code(out),
+                   _rows(out, "memory output"), step.num_seqs, heads, groups, head_dim, n_state, mode, chunk_len, max_chunks,
+                   carry.data_ptr() if carry is not None else None, carry.numel() if carry is not None else 0, self._stream())
+        self.launches += 3 if chunked else 1
+
     # ------------------------------------------------------------------ mixture of experts
+    def moe_route_scores(self, h, w_router, correction, top: int, groups: int, keep: int, experts, weights, norm_eps: float = 1e-20) -> None:
+        """Per token: scores = softmax over ALL router outputs (``w_router`` float32 ``[outputs, width]``, logits in 32-bit);
+        the ``top`` outputs with the largest ``score + correction`` among the ``keep`` best of ``groups`` equal runs of
+        neighbours (a run's score: its largest choice score) into ``experts``; their scores (without the correction) divided
+        by their sum ``+ norm_eps`` into ``weights``."""
+        self._dev(h, w_router, correction, experts, weights)
+        T, W = h.shape
+        E = w_router.shape[0]
+        if w_router.dtype != torch.float32 or not w_router.is_contiguous() or w_router.shape[1] != W or experts.dtype != torch.int32 \
+                or weights.dtype != torch.float32 or tuple(experts.shape) != (T, top) or tuple(weights.shape) != (T, top) \
+                or not experts.is_contiguous() or not weights.is_contiguous():
+            raise KernelError("moe_route_scores: float32 router [outputs, width], int32 experts and float32 weights [tokens, top] expected")
+        self._call("hb_moe_route_scores", h.data_ptr(), _code(h), _rows(h, "router input"), w_router.data_ptr(),
+                   self._f32_vec(correction, E, "router correction") if correction is not None else None, experts.data_ptr(),
+                   weights.data_ptr(), T, W, E, int(top), int(groups), int(keep), float(norm_eps), self._stream())
+        self.launches += 1
+
+    def gelu_unit(self, x, out, kind: str, row_gate: Optional[int] = None) -> None:
+        """``kind`` "tanh_gated": ``out = gelu_tanh(x[:, :F]) * x[:, F:2F]``; "erf": ``out = gelu_erf(x[:, :F])``, times
+        ``sigmoid(x[:, row_gate])`` when a column of ``x`` is named as the row's gate.  ``x`` float32."""
+        self._dev(x, out)
+        T, F = out.shape
+        code = {"tanh_gated": 0, "erf": 1}[kind]
+        if x.dtype != torch.float32 or x.shape[0] != T or x.shape[1] < (2 * F if code == 0 else F) or (row_gate is not None and not 0 <= row_gate < x.shape[1]):
+            raise KernelError("gelu_unit: float32 input rows that hold the unit's columns expected")
+        self._call("hb_gelu_unit", x.data_ptr(), _rows(x, "gelu_unit input"), out.data_ptr(), _code(out), _rows(out, "gelu_unit output"), T, F,
+                   code, -1 if row_gate is None else int(row_gate), self._stream())
+        self.launches += 1
+
     def moe_route(self, h, w_router, top: int, experts, weights) -> None:
         """Per token the ``top`` experts with the largest router logits (``w_router`` float32 ``[experts, width]``, logits in
         32-bit) into ``experts`` int32 ``[tokens, top]`` and the softmax over those logits into ``weights`` float32."""
@@ -1373,18 +1512,20 @@ class Ops:
         return int(self.lib.hb_moe_max_tiles(int(entries), int(n_experts), int(tile_rows)))
 
     def moe_experts(self, h, experts, weights, w_gate, w_up, w_down, limit: float, alpha: float, out, accumulate: bool, workspace,
-                    cap: int, tag: str = "") -> None:
+                    cap: int, tag: str = "", identity: bool = False) -> None:
         """``out (+)= sum_k weights[t, k] * expert_{experts[t, k]}(h[t])`` with the experts' weights stacked ``[experts, ff,
         width]`` (gate, up) and ``[experts, width, ff]`` (down) in the activations' dtype and the clamped gated unit of
         ``glu_clamp`` between them.  Four launches: plan, gate/up with activation, down, weighted sum.  bfloat16 operands whose
-        rows are multiples of 8 elements run the products on the tensor cores (``use_tensor_cores``), all others on the FP32 pipe."""
+        rows are multiples of 8 elements run the products on the tensor cores (``use_tensor_cores``), all others on the FP32 pipe.
+        ``w_up`` None: experts of one matrix, ``act = gelu_erf(w_gate h)`` (``limit`` and ``alpha`` unused).  ``identity``: expert
+        numbers from the stack's size on are identity experts, whose result is ``h[t]`` itself."""
         self._dev(h, experts, weights, w_gate, w_up, w_down, out)
         T, W = h.shape
         E, F = w_gate.shape[0], w_gate.shape[1]
         top = experts.shape[1]
-        if tuple(w_gate.shape) != (E, F, W) or tuple(w_up.shape) != (E, F, W) or tuple(w_down.shape) != (E, W, F) \
-                or not (w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous()) \
-                or not (w_gate.dtype == w_up.dtype == w_down.dtype == h.dtype):
+        if tuple(w_gate.shape) != (E, F, W) or (w_up is not None and tuple(w_up.shape) != (E, F, W)) or tuple(w_down.shape) != (E, W, F) \
+                or not (w_gate.is_contiguous() and (w_up is None or w_up.is_contiguous()) and w_down.is_contiguous()) \
+                or not (w_gate.dtype == w_down.dtype == h.dtype) or (w_up is not None and w_up.dtype != h.dtype):
             raise KernelError("moe_experts: stacked contiguous expert weights in the activations' dtype expected")
         if out.dtype != torch.float32 or tuple(out.shape) != (T, W):
             raise KernelError("moe_experts: float32 [tokens, width] output expected")
@@ -1400,13 +1541,15 @@ class Ops:
         down = workspace.buffer("moe.down" + tag, (most, W), torch.float32)
         s = self._stream()
         self._call("hb_moe_plan", experts.data_ptr(), entries, E, tile_rows, offsets.data_ptr(), order.data_ptr(), tiles.data_ptr(), s)
-        self._call("hb_moe_glu", h.data_ptr(), _code(h), _rows(h, "expert input"), w_gate.data_ptr(), w_up.data_ptr(), _code(w_gate),
+        self._call("hb_moe_glu", h.data_ptr(), _code(h), _rows(h, "expert input"), w_gate.data_ptr(),
+                   w_up.data_ptr() if w_up is not None else None, _code(w_gate),
                    offsets.data_ptr(), order.data_ptr(), tiles.data_ptr(), max_tiles, top, act.data_ptr(), _code(act), F, F, W,
                    float(limit), float(alpha), tc, s)
         self._call("hb_moe_down", act.data_ptr(), _code(act), F, w_down.data_ptr(), _code(w_down), offsets.data_ptr(), order.data_ptr(),
                    tiles.data_ptr(), max_tiles, top, down.data_ptr(), W, W, F, tc, s)
         self._call("hb_moe_combine", down.data_ptr(), W, weights.data_ptr(), top, out.data_ptr(), _rows(out, "expert output"), T, W,
-                   1 if accumulate else 0, s)
+                   1 if accumulate else 0, experts.data_ptr() if identity else None, E, h.data_ptr() if identity else None, _code(h),
+                   _rows(h, "expert input"), s)
         self.launches += 4
 
     def glu_clamp(self, gate_up, out, limit: float, alpha: float) -> None:

@@ -293,3 +293,62 @@ class PostNormBlock(Block):
         SandwichBlock._run(self.ff, y, (h, y, step))
         self.ff_post.add_normed(y, x, copy=ahead)
         return COPIED if ahead is not None else None
+
+
+@BLOCKS.register("prenorm_scaled")
+class ScaledPreNormBlock(Block):
+    """``x += m * mixer(norm_a(x))``, then, if the layer has a feed-forward, ``x += m * feed_forward(norm_b(x))``, with one
+    fixed factor ``m`` (the layer's ``block_params["residual_scale"]``) on every sublayer's result.  A sublayer writes its
+    result to a 32-bit buffer of the residual stream's shape (parts with ``can_overwrite`` write it, for others the buffer is
+    zeroed and they add); one kernel adds ``m`` times that buffer to the stream and, in the same pass, makes the next
+    norm's output from the values it still holds: the feed-forward's inside the layer, and across the seam the next layer's
+    first norm when that layer asks for it (``fold_request`` / ``prepare_next``, the protocol of the sandwich block)."""
+
+    ROLES = {"mixer_norm": NORMS, "mixer": MIXERS, "feed_forward_norm": NORMS, "feed_forward": FEED_FORWARDS}
+    OPTIONAL = ("feed_forward_norm", "feed_forward")
+    folds_norms = True
+
+    def __init__(self, layer_spec, ctx):
+        super().__init__(layer_spec, ctx)
+        p = self.parts
+        self.mixer_norm, self.mixer = p["mixer_norm"], p["mixer"]
+        self.ff_norm, self.ff = p.get("feed_forward_norm"), p.get("feed_forward")
+        if (self.ff is None) != (self.ff_norm is None):
+            raise ValueError(f"layer {layer_spec.prefix!r}: a feed-forward and its norm come together")
+        self.scale = float(layer_spec.block_params.get("residual_scale", 1.0))
+        self.fuse_norms = True              # tests switch it off to run every norm as a kernel of its own
+
+    def _h(self, step, size: int):
+        return self.ctx.workspace.buffer("block.h", (self.ctx.max_step_tokens, size), self.ctx.dtype)[:step.num_tokens]
+
+    def fold_request(self, step):
+        size = getattr(self.mixer_norm, "size", None)
+        if not self.fuse_norms or size is None:
+            return None
+        request = self.mixer_norm.fold_request(self._h(step, size))
+        return NormAhead(request) if request is not None else None
+
+    def _add(self, y, x, then) -> bool:
+        """``x += scale * y``; ``then`` (weight, offset, eps, out) of the norm that reads ``x`` next, or None."""
+        ops = self.ctx.ops
+        if then is not None and tuple(then[3].shape) == tuple(x.shape):
+            ops.scaled_add_norm(y, self.scale, x, then=(then[0], then[2], then[1]), then_out=then[3])
+            return True
+        ops.scaled_add_norm(y, self.scale, x)
+        return False
+
+    def forward(self, x, step, cache, state, append: bool, prepared=None, prepare_next=None):
+        ws, cap, T = self.ctx.workspace, self.ctx.max_step_tokens, step.num_tokens
+        h = self._h(step, x.shape[1])
+        y = ws.buffer("block.branch", (cap, x.shape[1]), torch.float32)[:T]
+        ahead = prepare_next if (self.fuse_norms and isinstance(prepare_next, NormAhead)) else None
+        if prepared is not NORMED:
+            self.mixer_norm.forward(x, h)
+        SandwichBlock._run(self.mixer, y, (h, y, step, cache, state, append))
+        if self.ff is None:
+            return NORMED if self._add(y, x, ahead) else None
+        request = self.ff_norm.fold_request(h) if self.fuse_norms else None
+        if not self._add(y, x, request):
+            self.ff_norm.forward(x, h)
+        SandwichBlock._run(self.ff, y, (h, y, step))
+        return NORMED if self._add(y, x, ahead) else None

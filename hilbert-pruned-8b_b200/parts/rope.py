@@ -13,6 +13,9 @@ YaRN (``yarn = {factor, original, fast, slow}``): with ``dim(t) = rot ln(origina
 ``f_i / factor * ramp_i + f_i (1 - ramp_i)``: fast pairs keep their frequency, slow ones are
 stretched, the band between is blended.  Cosines and sines are all multiplied by
 ``0.1 ln(factor) + 1``.
+
+Linear scaling (``linear = factor``): every frequency is divided by the factor (positions are stretched alike for all
+pairs); evaluated in 64-bit and rounded once to 32-bit.
 """
 from __future__ import annotations
 
@@ -82,7 +85,15 @@ class RotaryEmbedding(PositionEncoding):
         yarn = spec.get("yarn")
         if yarn is not None and spec.get("llama3") is not None:
             raise ValueError("rotary: llama3 and yarn scaling exclude each other")
-        if yarn is not None or spec.get("frequencies_in_64_bit"):
+        linear = spec.get("linear")
+        if linear is not None and (yarn is not None or spec.get("llama3") is not None):
+            raise ValueError("rotary: one kind of frequency scaling at a time")
+        if linear is not None:
+            if not float(linear) > 0.0:
+                raise ValueError("rotary: the linear scaling factor must be positive")
+            i = np.arange(self.rotary_dim // 2, dtype=np.float64)
+            self.inv_freq_host = (np.power(float(spec.params["theta"]), -2.0 * i / self.rotary_dim) / float(linear)).astype(np.float32)
+        elif yarn is not None or spec.get("frequencies_in_64_bit"):
             self.inv_freq_host = yarn_inv_freq(self.rotary_dim, float(spec.params["theta"]), yarn)
         else:
             self.inv_freq_host = rotary_inv_freq(self.rotary_dim, float(spec.params["theta"]), spec.get("llama3"))
