@@ -7,7 +7,9 @@ token-by-token loops, attention goes through an explicit mask, the experts are e
 token and picked afterwards.
 
 Notation: ``x`` residual stream, ``h`` a sublayer's normed input, ``S`` a recurrent state, ``m`` the
-factor on every sublayer's result (``x <- x + m * sublayer(norm(x))``).
+factor on every sublayer's result (``x <- x + m * sublayer(norm(x))``).  ``rnd`` rounds a tensor where the
+library rounds in bfloat16 (what a matrix product reads, queries, cached keys and values); the identity
+by default.
 """
 from __future__ import annotations
 
@@ -29,6 +31,14 @@ def rms_norm(x, w, eps: float):
 
 def silu(z):
     return z * torch.sigmoid(z)
+
+
+def same(t):
+    return t
+
+
+def to_bf16(t):
+    return t.to(torch.bfloat16).to(t.dtype)
 
 
 def softplus(z):
@@ -84,7 +94,7 @@ def head_state_scan(xs, B, C, dt, A, D):
     return y
 
 
-def mamba2_mixer(h, w: Dict[str, torch.Tensor], c: dict, eps: float):
+def mamba2_mixer(h, w: Dict[str, torch.Tensor], c: dict, eps: float, rnd=same):
     H, P, N, G = int(c["heads"]), int(c["vdim"]), int(c["state"]), int(c["groups"])
     inner = H * P
     T = h.shape[0]
@@ -99,7 +109,7 @@ def mamba2_mixer(h, w: Dict[str, torch.Tensor], c: dict, eps: float):
     y = y * silu(z)                                                  # the gate first, the norm after it
     parts = int(c["norm_groups"])
     y = rms_norm(y.reshape(T, parts, inner // parts), None, eps).reshape(T, inner) * w["norm"]
-    return y @ w["o"].T
+    return rnd(y) @ w["o"].T
 
 
 # ------------------------------------------------------------------------------------------------ chunked attention with a sink
@@ -141,7 +151,7 @@ def sink_softmax_attention(q, k, v, scale: float, mask, sink):
     return out
 
 
-def chunk_attention_mixer(h, w: Dict[str, torch.Tensor], c: dict, eps: float, positions):
+def chunk_attention_mixer(h, w: Dict[str, torch.Tensor], c: dict, eps: float, positions, rnd=same):
     H, G, d = int(c["heads"]), int(c["kv_heads"]), int(c["dim"])
     T = h.shape[0]
     q = (h @ w["q"].T + w["q.b"]).reshape(T, H, d)
@@ -154,8 +164,8 @@ def chunk_attention_mixer(h, w: Dict[str, torch.Tensor], c: dict, eps: float, po
         q = rotate_pairs(q, positions, int(rot["dims"]), float(rot["base"]), factor)
         k = rotate_pairs(k, positions, int(rot["dims"]), float(rot["base"]), factor)
     size = (c.get("mask") or {}).get("size")
-    o = sink_softmax_attention(q, k, v, float(c["scale"]), chunk_mask(T, size), w.get("sink"))
-    return o.reshape(T, H * d) @ w["o"].T
+    o = sink_softmax_attention(rnd(q), rnd(k), rnd(v), float(c["scale"]), chunk_mask(T, size), w.get("sink"))
+    return rnd(o.reshape(T, H * d)) @ w["o"].T
 
 
 # ------------------------------------------------------------------------------------------------ gated linear attention
@@ -171,7 +181,7 @@ def channel_decay_memory(q, k, v, alpha):
     return out
 
 
-def gated_linear_mixer(h, w: Dict[str, torch.Tensor], c: dict, eps: float):
+def gated_linear_mixer(h, w: Dict[str, torch.Tensor], c: dict, eps: float, rnd=same):
     H, d, dv = int(c["heads"]), int(c["dim"]), int(c["vdim"])
     T = h.shape[0]
     q = (h @ w["q"].T).reshape(T, H, d) * d ** -0.5
@@ -180,19 +190,19 @@ def gated_linear_mixer(h, w: Dict[str, torch.Tensor], c: dict, eps: float):
     zed = (h @ w["a1"].T) @ w["a2"].T + w["a2.b"]
     alpha = torch.pow(torch.sigmoid(zed), 1.0 / float(c["tau"])).reshape(T, H, d)
     o = rms_norm(channel_decay_memory(q, k, v, alpha), w["norm"], eps).reshape(T, H * dv)
-    return (o * silu(h @ w["g"].T)) @ w["o"].T
+    return rnd(o * silu(h @ w["g"].T)) @ w["o"].T
 
 
-def parallel_mixer(h, w: Dict[str, torch.Tensor], c: dict, eps: float, positions):
+def parallel_mixer(h, w: Dict[str, torch.Tensor], c: dict, eps: float, positions, rnd=same):
     sub = lambda side: {n[len(side) + 1:]: t for n, t in w.items() if n.startswith(side + ".")}
-    a = chunk_attention_mixer(h, sub("left"), c["left"], eps, positions)
-    b = gated_linear_mixer(h, sub("right"), c["right"], eps)
+    a = chunk_attention_mixer(h, sub("left"), c["left"], eps, positions, rnd)
+    b = gated_linear_mixer(h, sub("right"), c["right"], eps, rnd)
     return 0.5 * (rms_norm(a, w["left.out"], eps) + rms_norm(b, w["right.out"], eps))
 
 
 # ------------------------------------------------------------------------------------------------ feed-forwards
-def dense_ff(h, w):
-    return (gelu_tanh(h @ w["gate"].T) * (h @ w["up"].T)) @ w["down"].T
+def dense_ff(h, w, rnd=same):
+    return rnd(gelu_tanh(h @ w["gate"].T) * (h @ w["up"].T)) @ w["down"].T
 
 
 def route(h, w_router, correction, c: dict):
@@ -216,7 +226,7 @@ def route(h, w_router, correction, c: dict):
     return chosen, picked / (picked.sum(-1, keepdim=True) + 1e-20)
 
 
-def moe_ff(h, w, c: dict):
+def moe_ff(h, w, c: dict, rnd=same):
     r = c["router"]
     real = int(r["experts"])
     chosen, weights = route(h, w["router"], w["correction"], c)
@@ -226,10 +236,10 @@ def moe_ff(h, w, c: dict):
             if e >= real:
                 out[t] += g * h[t]                                   # an identity expert hands its input back
             else:
-                out[t] += g * (gelu_erf(h[t] @ w[f"e{e}.up"].T) @ w[f"e{e}.down"].T)
+                out[t] += g * (rnd(gelu_erf(h[t] @ w[f"e{e}.up"].T)) @ w[f"e{e}.down"].T)
     if c.get("shared") is not None:
-        y = gelu_erf(h @ w["shared.up"].T) @ w["shared.down"].T
-        out = out + torch.sigmoid(h @ w["shared.sg"].T) * y
+        # (the library multiplies the rows the second product reads by the gate: the same sum)
+        out = out + rnd(torch.sigmoid(h @ w["shared.sg"].T) * gelu_erf(h @ w["shared.up"].T)) @ w["shared.down"].T
     return out
 
 
@@ -250,36 +260,42 @@ def read_safetensors(path: str) -> Dict[str, torch.Tensor]:
 
 
 class PlainMoponex:
-    def __init__(self, model_dir: str, dtype=torch.float64):
-        with open(os.path.join(model_dir, "config.json")) as f:
-            self.cfg = json.load(f)
+    def __init__(self, cfg, tensors=None, dtype=torch.float64, round_to=None):
+        """``cfg``: the configuration (a dict) with ``tensors`` (name -> tensor), or a model folder."""
+        if tensors is None:
+            folder = cfg
+            with open(os.path.join(folder, "config.json")) as f:
+                cfg = json.load(f)
+            tensors = read_safetensors(os.path.join(folder, "model.safetensors"))
+        self.cfg = cfg
         self.dtype = dtype
-        self.w = {n: t.to(dtype) for n, t in read_safetensors(os.path.join(model_dir, "model.safetensors")).items()}
+        self.rnd = to_bf16 if round_to == torch.bfloat16 else same
+        self.w = {n: t.to(dtype) for n, t in tensors.items()}
 
     def _sub(self, prefix: str) -> Dict[str, torch.Tensor]:
         return {n[len(prefix):]: t for n, t in self.w.items() if n.startswith(prefix)}
 
     def logits(self, tokens: List[int], layers_out: Optional[list] = None):
         """[T, vocab] for the whole sequence; ``layers_out`` collects the stream after every layer."""
-        c, w = self.cfg, self.w
+        c, w, rnd = self.cfg, self.w, self.rnd
         eps, m = float(c["norm"]["eps"]), float(c.get("residual_mult", 1.0))
         pair = (c.get("embedding") or {}).get("bigram")
         x = embed(tokens, w["embed"], w.get("bigram"), pair)
         positions = torch.arange(len(tokens))
         for i, layer in enumerate(c["layers"]):
             p = f"l{i}."
-            h = rms_norm(x, w[p + "norm1"], eps)
+            h = rnd(rms_norm(x, w[p + "norm1"], eps))
             mw = self._sub(p + "mix.")
             if layer["type"] == "mamba2":
-                y = mamba2_mixer(h, mw, layer["mixer"], eps)
+                y = mamba2_mixer(h, mw, layer["mixer"], eps, rnd)
             else:
-                y = parallel_mixer(h, mw, layer["mixer"], eps, positions)
+                y = parallel_mixer(h, mw, layer["mixer"], eps, positions, rnd)
             x = x + m * y
             if layer.get("mlp") is not None:
-                h = rms_norm(x, w[p + "norm2"], eps)
+                h = rnd(rms_norm(x, w[p + "norm2"], eps))
                 fw = self._sub(p + "mlp.")
-                y = dense_ff(h, fw) if layer["mlp"]["kind"] == "dense" else moe_ff(h, fw, layer["mlp"])
+                y = dense_ff(h, fw, rnd) if layer["mlp"]["kind"] == "dense" else moe_ff(h, fw, layer["mlp"], rnd)
                 x = x + m * y
             if layers_out is not None:
                 layers_out.append(x.clone())
-        return (rms_norm(x, w["final.norm"], eps) @ w["embed"].T) * float(c.get("logit_scale", 1.0))
+        return (rnd(rms_norm(x, w["final.norm"], eps)) @ w["embed"].T) * float(c.get("logit_scale", 1.0))
