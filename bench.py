@@ -6,6 +6,7 @@
     python bench.py --design pogezen      # a line of its own: the Pogezen design beside Llama layers of equal size
     python bench.py --design vuladra      # a line of its own: the Vuladra design beside Pogezen layers of equal size
     python bench.py --design tonovik      # a line of its own: the Tonovik design beside Vuladra layers of equal size
+    python bench.py --design moponex      # a line of its own: the Moponex design beside Vuladra layers of equal size
 
 Prints ONE JSON line.  A step is one decode step of a batch of 8 sequences whose caches hold
 about 8192 tokens each; ``value`` is decoded tokens per second from CUDA events around the
@@ -468,6 +469,28 @@ def tonovik_config(z):
             "layers": [dict(lat, mlp=dense), dict(par, mlp=dense), dict(par, mlp=dense), dict(lat, mlp=dense)]}
 
 
+# --design moponex: four Moponex layers (state-space heads + dense gated feed-forward; chunked attention with a sink beside a
+# gated linear attention + mixture of experts, twice; state-space heads + mixture of experts) beside the four Vuladra layers
+# above, the library's closest model (a selective scan, two mixers side by side with a recurrent matrix memory, a mixture of
+# experts with a shared expert), at the same width, heads, head size and reach of the attention.  The state-space mixer has
+# twice the width as inner size in heads of 64 with 128 state values per channel (eight times the Vuladra scan's state);
+# the linear attention has the Vuladra memory's heads and sizes; the experts are 16 (and 2 identity experts, two groups of
+# which one is kept) of a quarter of the dense feed-forward's size, two chosen, with a shared expert of that size.
+def moponex_config(z):
+    W, hd = z["width"], z["head_dim"]
+    ssm = {"type": "mamba2", "mixer": {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": DESIGN_WINDOW},
+                 "rot": {"base": 500000.0, "dims": hd // 2, "scaling": {"factor": 8.0}}},
+        "right": {"heads": z["ml_heads"], "dim": z["ml_dim"], "vdim": W // z["ml_heads"], "tau": 16.0, "decay_rank": 16}}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "router": {"experts": VULADRA_EXPERTS, "top": VULADRA_TOP, "identity": 2, "groups": {"count": 2, "keep": 1}},
+           "expert": {"ff": z["ff"] // 4}, "shared": {"ff": z["ff"] // 4}}
+    return {"architecture": "Moponex", "embedding": {"bigram": {"buckets": 100003, "mul_prev": 1000003, "mul_cur": 10007}}, "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "logit_scale": 0.5, "vocab": DESIGN_VOCAB, "width": W,
+            "layers": [dict(ssm, mlp=dense), dict(par, mlp=moe), dict(par, mlp=moe), dict(ssm, mlp=moe)]}
+
+
 def llama_like_config(z):
     return dict(MODEL_8B, hidden_size=z["width"], num_hidden_layers=4, intermediate_size=z["ff"], vocab_size=DESIGN_VOCAB,
                 num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["head_dim"], tie_word_embeddings=True)
@@ -516,7 +539,9 @@ def design_comparison(a) -> int:
     out = {}
     for size, z in DESIGN_SIZES.items():
         row = {}
-        if a.design == "tonovik":
+        if a.design == "moponex":
+            pair = (("moponex", hb.MoponexConfig.from_dict(moponex_config(z))), ("vuladra", hb.VuladraConfig.from_dict(vuladra_config(z))))
+        elif a.design == "tonovik":
             pair = (("tonovik", hb.TonovikConfig.from_dict(tonovik_config(z))), ("vuladra", hb.VuladraConfig.from_dict(vuladra_config(z))))
         elif a.design == "vuladra":
             pair = (("vuladra", hb.VuladraConfig.from_dict(vuladra_config(z))), ("pogezen", hb.PogezenConfig.from_dict(pogezen_config(z))))
@@ -553,7 +578,7 @@ def design_comparison(a) -> int:
             del llm, eng, seqs
             torch.cuda.empty_cache()
         out[size] = row
-    names = {"tonovik": "Tonovik layers beside Vuladra layers", "vuladra": "Vuladra layers beside Pogezen layers",
+    names = {"moponex": "Moponex layers beside Vuladra layers", "tonovik": "Tonovik layers beside Vuladra layers", "vuladra": "Vuladra layers beside Pogezen layers",
              "pogezen": "Pogezen layers beside Llama layers"}[a.design]
     print(json.dumps({"metric": f"{names} of equal size: prefill of one 2048-token prompt and decode "
                                 f"steps of batch {batch} at context {context}, four layers, random weights",
@@ -658,7 +683,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=("8b", "3b", "1b"), default="8b",
                     help="8b: the default line; 3b, 1b: the generation workloads at those shapes (--steps = repeats)")
-    ap.add_argument("--design", choices=("pogezen", "vuladra", "tonovik"), default=None,
+    ap.add_argument("--design", choices=("pogezen", "vuladra", "tonovik", "moponex"), default=None,
                     help="a line of its own: this design's layers beside layers of equal size of the closest other design (prefill, decode, "
                          "device time per kernel); the default workload is not run")
     ap.add_argument("--timeline", action="store_true",
