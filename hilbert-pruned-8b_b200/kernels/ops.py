@@ -1420,7 +1420,7 @@ class Ops:
         self.launches += 3 if chunked else 1
 
     HEAD_SCAN_CHUNK_FROM = 256      # steps whose longest portion has at least so many tokens may run the memory in chunks
-    HEAD_SCAN_CHUNK = 64
+    HEAD_SCAN_CHUNK = 128
 
     def head_scan(self, u, k, q, decay_raw, decay_bias, state, step, out, heads: int, groups: int, head_dim: int, n_state: int,
                   a_log=None, inv_tau: float = 1.0, skip=None, z=None, q_scale: float = 1.0, workspace=None,
@@ -1444,9 +1444,12 @@ class Ops:
         if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != width * n_state or state.stride(1) != 1:
             raise KernelError("head_scan: state must be float32 [slots, heads * head_dim * n_state]")
         if chunked is None:
-            lanes = 4 if n_state <= 16 else min(32, n_state // 4)
+            # chunks walk every token twice: they pay only while one block per 64 channels of a head and sequence (the shape in
+            # which a thread holds the most state) would leave most SMs idle (measured, 2048 tokens of one sequence: 8 heads of
+            # 256 channels and 64 state values 371 us in chunks against 784 us; 8 heads of 512 channels and 128 state values
+            # 1323 against 1218 us; 128 heads of 64 channels 1937 against 1439 us)
             chunked = (workspace is not None and not step.is_decode and step.max_new >= self.HEAD_SCAN_CHUNK_FROM
-                       and -(-head_dim // (256 // max(lanes, 4))) * heads * step.num_seqs < self.sm_count)
+                       and -(-head_dim // 64) * heads * step.num_seqs < self.sm_count // 2)
         chunk_len, max_chunks, carry = 0, 0, None
         if chunked:
             chunk_len = self.HEAD_SCAN_CHUNK
