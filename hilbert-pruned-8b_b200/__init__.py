@@ -1,4 +1,4 @@
-"""A small generation library for one NVIDIA B200: the Llama 3 dense decoder, the Pogezen, Vuladra and Tonovik decoders.
+"""A small generation library for one NVIDIA B200: the Llama 3 dense decoder, the Pogezen, Vuladra, Tonovik and Moponex decoders.
 
 Everything between a request's token ids and its next token: typed configuration and
 architecture registry, weights by tensor name, layers put together from parts, a paged
