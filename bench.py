@@ -474,20 +474,20 @@ def tonovik_config(z):
 # above, the library's closest model (a selective scan, two mixers side by side with a recurrent matrix memory, a mixture of
 # experts with a shared expert), at the same width, heads, head size and reach of the attention.  The state-space mixer has
 # twice the width as inner size in heads of 64 with 128 state values per channel (eight times the Vuladra scan's state);
-# the linear attention has the Vuladra memory's heads and sizes; the experts are 16 (and 2 identity experts, two groups of
-# which one is kept) of a quarter of the dense feed-forward's size, two chosen, with a shared expert of that size.
+# the linear attention has the Vuladra memory's heads and sizes; the experts are 16 (and 4 identity experts, four groups of
+# which two are kept) of a quarter of the dense feed-forward's size, two chosen, with a shared expert of that size.
 def moponex_config(z):
     W, hd = z["width"], z["head_dim"]
     ssm = {"type": "mamba2", "mixer": {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}}
     par = {"type": "parallel", "mixer": {
         "left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": DESIGN_WINDOW},
                  "rot": {"base": 500000.0, "dims": hd // 2, "scaling": {"factor": 8.0}}},
-        "right": {"heads": z["ml_heads"], "dim": z["ml_dim"], "vdim": W // z["ml_heads"], "tau": 16.0, "decay_rank": 16}}}
+        "right": {"heads": z["ml_heads"], "dim": z["ml_dim"], "vdim": W // z["ml_heads"], "tau": 8.0, "decay_rank": 32}}}
     dense = {"kind": "dense", "ff": z["ff"]}
-    moe = {"kind": "moe", "router": {"experts": VULADRA_EXPERTS, "top": VULADRA_TOP, "identity": 2, "groups": {"count": 2, "keep": 1}},
+    moe = {"kind": "moe", "router": {"experts": VULADRA_EXPERTS, "top": VULADRA_TOP, "identity": 4, "groups": {"count": 4, "keep": 2}},
            "expert": {"ff": z["ff"] // 4}, "shared": {"ff": z["ff"] // 4}}
     return {"architecture": "Moponex", "embedding": {"bigram": {"buckets": 100003, "mul_prev": 1000003, "mul_cur": 10007}}, "norm": {"eps": 1e-6},
-            "residual_mult": 0.5, "logit_scale": 0.5, "vocab": DESIGN_VOCAB, "width": W,
+            "residual_mult": 0.7, "logit_scale": 0.8, "vocab": DESIGN_VOCAB, "width": W,
             "layers": [dict(ssm, mlp=dense), dict(par, mlp=moe), dict(par, mlp=moe), dict(ssm, mlp=moe)]}
 
 

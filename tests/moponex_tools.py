@@ -74,10 +74,10 @@ EDGES = config(48, 130, [
 # exactly one page and chunks that straddle pages; states of 64 and 128; experts whose sizes the tensor-core tiles take
 WIDE = config(128, 300, [
     with_mlp(mamba2(4, 32, 64, groups=2), moe(8, 2, 64, identity=0, groups=(2, 1), shared=64)),
-    with_mlp(parallel((2, 1, 64, 64, (32, 10000.0, 2.0)), (2, 64, 32, 16.0, 8)), dense(192)),
+    with_mlp(parallel((2, 1, 64, 64, (16, 10000.0, 4.0)), (2, 64, 32, 12.0, 8)), dense(192)),
     with_mlp(mamba2(2, 64, 128, norm_groups=2), None),
     with_mlp(parallel((16, 4, 64, 70, (64, 500.0, None)), (4, 32, 32, 4.0, 16)), moe(6, 2, 32, identity=2, groups=(4, 3))),
-    with_mlp(parallel((2, 2, 128, 100, (16, 100.0, 8.0)), (1, 128, 64, 32.0, 8)), dense(64))], bigram=(509, 127, 17))
+    with_mlp(parallel((2, 2, 128, 100, (16, 100.0, 8.0)), (1, 128, 64, 32.0, 8)), dense(64))], bigram=(997, 1000003, 31))
 
 CONFIGS = {"mixed": MIXED, "edges": EDGES, "wide": WIDE}
 

@@ -319,7 +319,7 @@ def _close(got, want, dtype, what):
         assert err.max() < (1e-4 if dtype == torch.float32 else 3e-2), f"{what}: sequence {i} position {int(err.argmax())}: {float(err.max()):.3e}"
 
 
-SSM = [(4, 8, 16, 2, 3, 2), (1, 8, 1, 1, 1, 1), (4, 4, 4, 4, 5, 4), (2, 64, 128, 1, 4, 2), (6, 48, 40, 3, 4, 1), (3, 20, 100, 1, 2, 3), (8, 16, 256, 2, 4, 1)]
+SSM = [(4, 8, 16, 2, 3, 2), (1, 8, 1, 1, 1, 1), (4, 4, 4, 4, 5, 4), (2, 64, 128, 1, 4, 2), (6, 40, 48, 3, 3, 1), (3, 20, 100, 1, 2, 3), (8, 16, 256, 2, 4, 1)]
 
 
 @pytest.mark.gpu
@@ -390,7 +390,7 @@ def _selection(rows, width, at):
 
 # (heads, kv heads, dim, chunk, rotated dims): the general kernel, the one-block-per-token kernel in its variants, the
 # tensor-core prompt kernel (key heads of 64 and 128 in bfloat16), sixteen heads (weights times values on the tensor cores)
-CHUNKS = [(4, 2, 16, 20, 8), (1, 1, 8, 1, 0), (3, 3, 4, 1000, 4), (2, 1, 64, 64, 32), (16, 4, 64, 70, 64), (2, 2, 128, 100, 16), (6, 2, 24, 63, 24),
+CHUNKS = [(4, 2, 16, 20, 8), (1, 1, 8, 1, 0), (3, 3, 4, 1000, 4), (2, 1, 64, 64, 16), (16, 4, 64, 70, 64), (2, 2, 128, 100, 16), (6, 2, 24, 63, 24),
           (5, 1, 12, 65, 6), (2, 1, 64, None, 64)]
 
 
