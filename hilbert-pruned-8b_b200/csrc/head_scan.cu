@@ -33,7 +33,7 @@ __device__ __forceinline__ float hs_softplus(float z) { return z > 20.0f ? z : l
 // staged k, q and decay rows are read by 16-byte loads and the sum over n needs log2(LANES) shuffles per token.  Rows are
 // staged with zeros behind index N: the walk has no bounds checks.
 template <typename TO, int LANES, int PER>
-__global__ void __launch_bounds__(HS_THREADS)
+__global__ void __launch_bounds__(HS_THREADS, PER <= 8 ? 4 : 2)
 head_scan_kernel(const float* __restrict__ u, long long ldu, const float* __restrict__ kmat, long long ldk,
                  const float* __restrict__ qmat, long long ldq, const float* __restrict__ z, long long ldz,
                  const float* __restrict__ draw, long long ldd, const float* __restrict__ dbias, const float* __restrict__ a_log,
@@ -45,6 +45,7 @@ head_scan_kernel(const float* __restrict__ u, long long ldu, const float* __rest
     // the decays' logarithms out; 3: that chunk from carry_S0, with outputs (head_scan_carry wrote the state)
     pdl_trigger();
     constexpr int CH = HS_THREADS / LANES, RS = LANES * (PER + HS_PAD), NP = LANES * PER;
+    constexpr int HS_STAGE = PER <= 8 ? 4 : 8;     // loads of k, q and decay inputs a thread issues before it uses the first
     extern __shared__ __align__(16) float hs_smem[];
     const int EW = decay_mode ? RS : 4;            // floats per token of the decay rows
     float* ks = hs_smem;                           // [HS_TOK][RS]: s * k
@@ -136,25 +137,35 @@ head_scan_kernel(const float* __restrict__ u, long long ldu, const float* __rest
             }
             __syncthreads();
         }
-        for (int i = tid; i < nt * NP; i += HS_THREADS) {
-            const int r = i / NP, n = i - r * NP;
-            const int at = r * RS + (n / PER) * (PER + HS_PAD) + n % PER;
-            const size_t t = (size_t)(start + base + r);
-            float kv = 0.0f, qv = 0.0f;
-            if (n < N) {
-                kv = kmat[t * ldk + (size_t)g * N + n];
-                qv = qmat[t * ldq + (size_t)g * N + n];
+        // the tokens' k, q and decay inputs: HS_STAGE loads of a thread in flight before the first is used
+        for (int i0 = tid; i0 < nt * NP; i0 += HS_THREADS * HS_STAGE) {
+            float kv[HS_STAGE], qv[HS_STAGE], dr[HS_STAGE];
+#pragma unroll
+            for (int s8 = 0; s8 < HS_STAGE; s8++) {
+                const int i = i0 + s8 * HS_THREADS, r = i / NP, n = i - r * NP;
+                kv[s8] = qv[s8] = dr[s8] = 0.0f;
+                if (i < nt * NP && n < N) {
+                    const size_t t = (size_t)(start + base + r);
+                    kv[s8] = kmat[t * ldk + (size_t)g * N + n];
+                    qv[s8] = qmat[t * ldq + (size_t)g * N + n];
+                    if (decay_mode) dr[s8] = draw[t * ldd + (size_t)h * N + n] + dbias[(size_t)h * N + n];
+                }
             }
-            if (decay_mode == 0) {
-                kv *= ds[r];
-            } else {
-                float lg = 0.0f;
-                if (n < N) lg = -hs_softplus(-(draw[t * ldd + (size_t)h * N + n] + dbias[(size_t)h * N + n])) * inv_tau;   // log(sigmoid) / tau
-                ls[i] = lg;
-                es[at] = expm1f(lg);
+#pragma unroll
+            for (int s8 = 0; s8 < HS_STAGE; s8++) {
+                const int i = i0 + s8 * HS_THREADS, r = i / NP, n = i - r * NP;
+                if (i >= nt * NP) break;
+                const int at = r * RS + (n / PER) * (PER + HS_PAD) + n % PER;
+                if (decay_mode == 0) {
+                    kv[s8] *= ds[r];
+                } else {
+                    const float lg = n < N ? -hs_softplus(-dr[s8]) * inv_tau : 0.0f;      // log(sigmoid) / tau
+                    ls[i] = lg;
+                    es[at] = expm1f(lg);
+                }
+                ks[at] = kv[s8];
+                qs[at] = qv[s8];
             }
-            ks[at] = kv;
-            qs[at] = qv;
         }
         for (int i = tid; i < nt * CH; i += HS_THREADS) {
             const int r = i / CH, c = i - r * CH, jj = blockIdx.x * CH + c;

@@ -1446,8 +1446,8 @@ class Ops:
         if chunked is None:
             # chunks walk every token twice: they pay only while one block per 64 channels of a head and sequence (the shape in
             # which a thread holds the most state) would leave most SMs idle (measured, 2048 tokens of one sequence: 8 heads of
-            # 256 channels and 64 state values 371 us in chunks against 784 us; 8 heads of 512 channels and 128 state values
-            # 1323 against 1218 us; 128 heads of 64 channels 1937 against 1439 us)
+            # 256 channels and 64 state values 354 us in chunks against 843 us; 8 heads of 512 channels and 128 state values
+            # 1168 against 1319 us; 64 heads of 64 channels 972 against 1001 us; 128 heads of 64 channels 1704 against 1418 us)
             chunked = (workspace is not None and not step.is_decode and step.max_new >= self.HEAD_SCAN_CHUNK_FROM
                        and -(-head_dim // 64) * heads * step.num_seqs < self.sm_count // 2)
         chunk_len, max_chunks, carry = 0, 0, None
